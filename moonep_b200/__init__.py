@@ -2,3 +2,13 @@
 from .plan import CommPlan  # noqa: F401
 
 __version__ = "0.1.0"
+__all__ = ["Buffer", "CommPlan", "CommTimeoutError"]
+
+
+def __getattr__(name):
+    # Buffer pulls in torch.distributed and the native library; import it lazily so that
+    # `import moonep_b200` stays cheap for users of the CPU oracle only.
+    if name in ("Buffer", "CommTimeoutError", "destroy_live_buffers"):
+        from . import api
+        return getattr(api, name)
+    raise AttributeError(name)

@@ -1,0 +1,289 @@
+// Combine: local fp32 pre-reduction of duplicate rows, then every rank PULLS the rows of its
+// own tokens from the peers' shards and sums them in fp32 in ascending k.
+//
+// Reference counterparts: CombinePrologueKernel (moonep/combine_prologue.py:196-484) and
+// CombineKernel (moonep/combine.py:210-511).  The sum is unweighted, as in the reference:
+// the route weights travel with dispatch so that the expert FFN can apply them.
+// Rounding points are the same as in the CPU simulator (ref/sim_ref.cc): one bf16 rounding
+// of each pre-reduced primary row, one of the final sum; additions are fp32 in chain / k
+// order, so results are bitwise reproducible.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common/layout.h"
+#include "device/sync.cuh"
+#include "device/tma.cuh"
+#include "host/ctx.h"
+#include "host/errors.h"
+
+namespace mep {
+
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ uint4 f32_to_bf16x8(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ---- prologue: primary += duplicates (local) ---------------------------------------------
+struct PrologueParams {
+  int H, epn;
+  int64_t NvS, hidden_stride;
+  int rank_base;
+  __nv_bfloat16* hidden;
+  const int32_t* link;        // [Rv][NvS]
+  const int32_t* cu_seqlens;  // [Rv][2epn]
+};
+
+constexpr int PROLOGUE_THREADS = 256;
+
+__global__ void __launch_bounds__(PROLOGUE_THREADS) ep_combine_prologue_kernel(const PrologueParams p) {
+  __shared__ int chain[PROLOGUE_THREADS / 32][MAX_TOPK];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vr = blockIdx.y, rank = p.rank_base + vr;
+  const int32_t* link = p.link + (size_t)vr * p.NvS;
+  int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
+  if (rows > p.NvS) rows = p.NvS;
+  uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
+  const int nvec = p.H / 8;
+  const int64_t nwarps = (int64_t)gridDim.x * (PROLOGUE_THREADS / 32);
+  for (int64_t r = (int64_t)blockIdx.x * (PROLOGUE_THREADS / 32) + warp; r < rows; r += nwarps) {
+    int l = link[r];
+    if ((l & LINK_DUP_BIT) != 0) continue;
+    int next = l & LINK_NEXT_MASK;
+    if (next == LINK_NONE) continue;
+    int n = 0;
+    if (lane == 0) {
+      while (next != LINK_NONE && next < rows && n < MAX_TOPK - 1) {
+        chain[warp][n++] = next;
+        next = link[next] & LINK_NEXT_MASK;
+      }
+    }
+    n = __shfl_sync(0xffffffffu, n, 0);
+    __syncwarp();
+    uint4* prim = shard + (size_t)r * nvec;
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8], t[8];
+      bf16x8_to_f32(prim[v], acc);
+      for (int i = 0; i < n; ++i) {
+        bf16x8_to_f32(shard[(size_t)chain[warp][i] * nvec + v], t);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += t[q];
+      }
+      prim[v] = f32_to_bf16x8(acc);
+    }
+    __syncwarp();
+  }
+}
+
+// ---- combine: remote pull + K-way fp32 sum -----------------------------------------------
+struct CombineParams {
+  SyncCtx sync;
+  int S, K, H;
+  int64_t N, NvS, hidden_stride, weights_off;
+  const int32_t* dst;            // [Rv][N]
+  const __nv_bfloat16* hidden;   // symmetric base
+  __nv_bfloat16* out;            // [Rv][S][H]
+  float* w_out;                  // [Rv][S][K] or null
+};
+
+constexpr int COMBINE_ACC_THREADS = 128;
+constexpr int COMBINE_THREADS = 32 + COMBINE_ACC_THREADS + 32;  // loader, 4 acc warps, weights
+
+__device__ __forceinline__ void named_bar_sync(int id, int n) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
+// NV: 16-byte vectors per accumulator thread (H <= NV * 128 * 8)
+template <int ST, int NV>
+__global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const CombineParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full[ST];
+  __shared__ __align__(8) uint64_t empty[ST];
+  __shared__ int last_flag[ST];
+  const SyncCtx& sc = p.sync;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int vr = blockIdx.y;
+  const int G = gridDim.x, c = blockIdx.x;
+  const uint32_t row_bytes = (uint32_t)p.H * 2u;
+  const int nvec = p.H / 8;
+  uint8_t* ring = smem_raw;
+  uint8_t* out_stage = smem_raw + (size_t)ST * row_bytes;
+
+  if (tid == 0) {
+    for (int s = 0; s < ST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], COMBINE_ACC_THREADS / 32); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  cross_rank_barrier(sc, 1);  // every rank's shard (and its pre-reduction) is final
+
+  const int32_t* dst = p.dst + (size_t)vr * p.N;
+  const int n_tok = c < p.S ? (p.S - c + G - 1) / G : 0;
+
+  if (warp == 0) {
+    // ---- loader: one remote bulk read per primary entry -----------------------------------
+    int prod = 0;
+    for (int j = 0; j < n_tok; ++j) {
+      const int t = c + j * G;
+      int d = lane < p.K ? dst[(size_t)t * p.K + lane] : -1;
+      unsigned prim = __ballot_sync(0xffffffffu, d >= 0);
+      while (prim) {
+        int k = __ffs(prim) - 1;
+        prim &= prim - 1;
+        int dk = __shfl_sync(0xffffffffu, d, k);
+        if (lane == 0) {
+          const int s = prod % ST;
+          if (prod >= ST) mbar_wait(sc, &empty[s], ((uint32_t)(prod / ST) & 1u) ^ 1u, 20);
+          int64_t dr = dk / p.NvS, row = dk - dr * p.NvS;
+          if (dr >= sc.R) { report_failure(sc, ST_BAD_INDEX, 21, (int)dr, dk, (int)p.NvS); dr = 0; }
+          last_flag[s] = prim == 0;
+          mbar_expect_tx(&full[s], row_bytes);
+          bulk_g2s(ring + (size_t)s * row_bytes,
+                   p.hidden + ((size_t)dr * p.hidden_stride + row) * p.H, row_bytes, &full[s]);
+        }
+        ++prod;
+      }
+    }
+  } else if (warp <= COMBINE_ACC_THREADS / 32) {
+    // ---- accumulators ----------------------------------------------------------------------
+    const int ta = tid - 32;
+    __nv_bfloat16* out = p.out + (size_t)vr * p.S * p.H;
+    int cons = 0;
+    for (int j = 0; j < n_tok; ++j) {
+      float acc[NV][8];
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
+      for (int guard = 0; guard < MAX_TOPK; ++guard) {
+        const int s = cons % ST;
+        bool ok = mbar_wait(sc, &full[s], (uint32_t)(cons / ST) & 1u, 30);
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+        const int is_last = ok ? last_flag[s] : 1;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          int v = ta + i * COMBINE_ACC_THREADS;
+          if (v < nvec) {
+            float t[8];
+            bf16x8_to_f32(src[v], t);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc[i][q] += t[q];
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+        ++cons;
+        if (is_last) break;
+      }
+      // stage the bf16 row and hand it to one bulk store
+      uint8_t* os = out_stage + (size_t)(j & 1) * row_bytes;
+      if (j >= 2) {
+        if (ta == 0) bulk_wait_read<1>();
+        named_bar_sync(1, COMBINE_ACC_THREADS);
+      }
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        int v = ta + i * COMBINE_ACC_THREADS;
+        if (v < nvec) reinterpret_cast<uint4*>(os)[v] = f32_to_bf16x8(acc[i]);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1, COMBINE_ACC_THREADS);
+      if (ta == 0) {
+        bulk_s2g(out + (size_t)(c + (int64_t)j * G) * p.H, os, row_bytes);
+        bulk_commit();
+      }
+    }
+    if (ta == 0) bulk_wait<0>();
+  } else if (p.w_out != nullptr) {
+    // ---- route weights back to token-major, raw 32-bit words -------------------------------
+    float* w_out = p.w_out + (size_t)vr * p.N;
+    const int64_t n_ent = (int64_t)n_tok * p.K;
+    for (int64_t i = lane; i < n_ent; i += 32) {
+      int j = (int)(i / p.K), k = (int)(i - (int64_t)j * p.K);
+      int64_t e = (int64_t)(c + (int64_t)j * G) * p.K + k;
+      int d = dst[e];
+      int64_t raw = d >= 0 ? d : -(int64_t)d - 1;
+      int64_t dr = raw / p.NvS, row = raw - dr * p.NvS;
+      int bits = dr < sc.R ? sc.meta[(size_t)dr * sc.meta_stride + p.weights_off + row] : 0;
+      w_out[e] = __int_as_float(bits);
+    }
+  }
+}
+
+template <int ST, int NV>
+static int launch_combine_t(const BufferCtx& c, CombineParams& p, size_t smem, cudaStream_t stream) {
+  static thread_local size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_combine_kernel<ST, NV>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(c.num_sms, c.Rv());
+  MEP_CUDA_OK(launch_coop((const void*)ep_combine_kernel<ST, NV>, grid, dim3(COMBINE_THREADS), smem,
+                          stream, p));
+  return 0;
+}
+
+template <int NV>
+static int launch_combine_nv(const BufferCtx& c, CombineParams& p, cudaStream_t stream) {
+  const size_t row = (size_t)c.H * 2;
+  const size_t budget = c.virt ? 100 * 1024 : 210 * 1024;
+  if (14 * row <= budget) return launch_combine_t<12, NV>(c, p, 14 * row, stream);
+  if (10 * row <= budget) return launch_combine_t<8, NV>(c, p, 10 * row, stream);
+  if (6 * row <= budget) return launch_combine_t<4, NV>(c, p, 6 * row, stream);
+  if (4 * row <= 220 * 1024) return launch_combine_t<2, NV>(c, p, 4 * row, stream);
+  return fail(-2, "combine: H=%d does not fit a 2-stage ring", c.H);
+}
+
+}  // namespace mep
+
+using namespace mep;
+
+extern "C" {
+
+int mep_launch_combine_prologue(const void* ctx_, const int32_t* link, const int32_t* cu_seqlens,
+                                cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  PrologueParams p;
+  p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
+  p.rank_base = c.virt ? 0 : c.rank;
+  p.hidden = (__nv_bfloat16*)c.hidden; p.link = link; p.cu_seqlens = cu_seqlens;
+  dim3 grid(c.num_sms_local, c.Rv());
+  ep_combine_prologue_kernel<<<grid, PROLOGUE_THREADS, 0, stream>>>(p);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// dst [Rv][N], out [Rv][S][H] bf16, w_out [Rv][S][K] fp32 or null.
+int mep_launch_combine(const void* ctx_, const int32_t* dst, void* out, float* w_out,
+                       cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  if (c.H % 8 != 0) return fail(-1, "combine needs H %% 8 == 0 (got %d)", c.H);
+  CombineParams p;
+  p.sync = c.sync(KID_COMBINE);
+  p.S = c.S; p.K = c.K; p.H = c.H; p.N = c.N; p.NvS = c.NvS;
+  p.hidden_stride = c.hidden_stride; p.weights_off = c.ml.weights_off;
+  p.dst = dst; p.hidden = (const __nv_bfloat16*)c.hidden;
+  p.out = (__nv_bfloat16*)out; p.w_out = w_out;
+  const int nvec = c.H / 8;
+  const int nv = (nvec + COMBINE_ACC_THREADS - 1) / COMBINE_ACC_THREADS;
+  if (nv <= 1) return launch_combine_nv<1>(c, p, stream);
+  if (nv <= 2) return launch_combine_nv<2>(c, p, stream);
+  if (nv <= 4) return launch_combine_nv<4>(c, p, stream);
+  if (nv <= 7) return launch_combine_nv<7>(c, p, stream);
+  if (nv <= 16) return launch_combine_nv<16>(c, p, stream);
+  return fail(-3, "combine: H=%d is larger than 16384", c.H);
+}
+
+}  // extern "C"

@@ -1,0 +1,258 @@
+// Dispatch: fused permute + all-to-all of bf16 token rows and fp32 route weights, written
+// straight into their expert-grouped slots in the destination ranks' buffers, plus the local
+// duplicate expansion that follows it.
+//
+// Reference counterparts: DispatchKernel (moonep/dispatch.py:268-692) and
+// DispatchEpilogueKernel (moonep/dispatch_epilogue.py:167-304).  Here:
+//  * each row is staged once in shared memory by a 1-D bulk copy and then bulk-stored to at
+//    most one slot per destination rank; the K stores of a row are issued by K lanes in
+//    parallel, each tracking its own bulk group;
+//  * there is no dedup builder: the chain links were written by the planner (source side);
+//    the kernel only snapshots this rank's links into the plan after its exit barrier;
+//  * padding rows are zeroed with bulk stores from one zero row, and their weight and link
+//    slots are reset locally.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "common/layout.h"
+#include "device/sync.cuh"
+#include "device/tma.cuh"
+#include "host/ctx.h"
+#include "host/errors.h"
+
+namespace mep {
+
+struct DispatchParams {
+  SyncCtx sync;
+  int S, K, H, epn;
+  int64_t N, NvS, hidden_stride, weights_off, link_off;
+  const __nv_bfloat16* x;     // [Rv][S][H]
+  const float* w;             // [Rv][S][K] or null
+  const int32_t* dst;         // [Rv][N]
+  const int32_t* zero_fill;   // [Rv][2epn][2]
+  __nv_bfloat16* hidden;      // symmetric, chunk of rank 0
+  int32_t* link_out;          // [Rv][NvS] or null
+  int entry_barrier;
+  int fresh;                  // plan made by the preceding planner launch
+};
+
+constexpr int DISPATCH_THREADS = 128;
+
+template <int ST>
+__global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const DispatchParams p) {
+  constexpr int LA = ST / 2;  // loads kept in flight; the other half of the ring drains stores
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full[ST];
+  const SyncCtx& sc = p.sync;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int vr = blockIdx.y, rank = sc.rank_base + vr;
+  const int G = gridDim.x, c = blockIdx.x;
+  const uint32_t row_bytes = (uint32_t)p.H * 2u;
+  uint8_t* ring = smem_raw;
+  uint8_t* zero_row = smem_raw + (size_t)ST * row_bytes;
+
+  if (tid == 0) {
+    for (int s = 0; s < ST; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
+  }
+  for (uint32_t i = tid * 16u; i < row_bytes; i += DISPATCH_THREADS * 16u)
+    *reinterpret_cast<uint4*>(zero_row + i) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (p.entry_barrier) cross_rank_barrier(sc, 1);
+
+  const __nv_bfloat16* x = p.x + (size_t)vr * p.S * p.H;
+  const int32_t* dst = p.dst + (size_t)vr * p.N;
+  const int n_tok = c < p.S ? (p.S - c + G - 1) / G : 0;
+
+  if (warp == 0) {
+    // ---- rows: load once, store to every destination rank that needs the payload --------
+    if (lane == 0) {
+      for (int j = 0; j < LA && j < n_tok; ++j) {
+        mbar_expect_tx(&full[j], row_bytes);
+        bulk_g2s(ring + (size_t)j * row_bytes, x + (size_t)(c + (int64_t)j * G) * p.H, row_bytes,
+                 &full[j]);
+      }
+    }
+    __syncwarp();
+    for (int j = 0; j < n_tok; ++j) {
+      const int s = j % ST;
+      const int t = c + j * G;
+      int d = lane < p.K ? dst[(size_t)t * p.K + lane] : -1;
+      mbar_wait(sc, &full[s], (uint32_t)(j / ST) & 1u, 10);
+      if (d >= 0) {
+        int64_t dr = d / p.NvS, row = d - dr * p.NvS;
+        if (dr < sc.R) {
+          bulk_s2g(p.hidden + ((size_t)dr * p.hidden_stride + row) * p.H,
+                   ring + (size_t)s * row_bytes, row_bytes);
+        } else {
+          report_failure(sc, ST_BAD_INDEX, 11, (int)dr, d, (int)p.NvS);
+        }
+      }
+      bulk_commit();
+      if (j + LA < n_tok) {
+        // the stage to refill was last read by the stores of token j + LA - ST
+        bulk_wait_read<ST - LA>();
+        __syncwarp();
+        if (lane == 0) {
+          const int s2 = (j + LA) % ST;
+          mbar_expect_tx(&full[s2], row_bytes);
+          bulk_g2s(ring + (size_t)s2 * row_bytes, x + (size_t)(c + (int64_t)(j + LA) * G) * p.H,
+                   row_bytes, &full[s2]);
+        }
+      }
+    }
+    bulk_wait<0>();
+    fence_proxy_async();
+  } else if (warp == 1) {
+    // ---- route weights: one 4-byte store per (token, k), duplicates included -------------
+    if (p.w != nullptr) {
+      const float* w = p.w + (size_t)vr * p.N;
+      const int64_t n_ent = (int64_t)n_tok * p.K;
+      for (int64_t i = lane; i < n_ent; i += 32) {
+        int j = (int)(i / p.K), k = (int)(i - (int64_t)j * p.K);
+        int64_t e = (int64_t)(c + (int64_t)j * G) * p.K + k;
+        int d = dst[e];
+        int64_t raw = d >= 0 ? d : -(int64_t)d - 1;
+        int64_t dr = raw / p.NvS, row = raw - dr * p.NvS;
+        if (dr < sc.R)
+          sc.meta[(size_t)dr * sc.meta_stride + p.weights_off + row] = __float_as_int(w[e]);
+      }
+    }
+  } else {
+    // ---- padding rows of MY shard: zero payload, weight 0, link NONE ----------------------
+    const int32_t* zf = p.zero_fill + (size_t)vr * 2 * p.epn * 2;
+    int32_t* my_meta = sc.meta + (size_t)rank * sc.meta_stride;
+    __nv_bfloat16* my_shard = p.hidden + (size_t)rank * p.hidden_stride * p.H;
+    int pending = 0;
+    for (int g = 0; g < 2 * p.epn; ++g) {
+      const int first = zf[2 * g], n = zf[2 * g + 1];
+      if (n <= 0 || first < 0 || (int64_t)first + n > p.NvS) continue;
+      if (warp == 2) {
+        // one elected thread issues the row stores of this CTA's share
+        if (lane == 0) {
+          for (int r = first + c; r < first + n; r += G) {
+            bulk_s2g(my_shard + (size_t)r * p.H, zero_row, row_bytes);
+            if (++pending == 16) { bulk_commit(); bulk_wait_read<4>(); pending = 0; }
+          }
+        }
+      } else {
+        for (int r = first + c * 32 + lane; r < first + n; r += G * 32) {
+          if (p.w != nullptr) my_meta[p.weights_off + r] = 0;
+          if (p.fresh) my_meta[p.link_off + r] = LINK_NONE;
+        }
+      }
+    }
+    if (warp == 2 && lane == 0) { bulk_commit(); bulk_wait<0>(); fence_proxy_async(); }
+  }
+  fence_sys();
+  cross_rank_barrier(sc, 2);
+
+  if (p.link_out != nullptr) {
+    const int32_t* src = sc.meta + (size_t)rank * sc.meta_stride + p.link_off;
+    int32_t* out = p.link_out + (size_t)vr * p.NvS;
+    for (int64_t i = (int64_t)c * DISPATCH_THREADS + tid; i < p.NvS; i += (int64_t)G * DISPATCH_THREADS)
+      out[i] = src[i];
+  }
+}
+
+// ---- duplicate expansion (local) ---------------------------------------------------------
+struct ExpandParams {
+  int H, epn;
+  int64_t NvS, hidden_stride;
+  int rank_base;
+  __nv_bfloat16* hidden;       // symmetric base
+  const int32_t* link;         // [Rv][NvS] plan-owned
+  const int32_t* cu_seqlens;   // [Rv][2epn]
+};
+
+constexpr int EXPAND_THREADS = 256;
+
+__global__ void __launch_bounds__(EXPAND_THREADS) ep_expand_kernel(const ExpandParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vr = blockIdx.y, rank = p.rank_base + vr;
+  const int32_t* link = p.link + (size_t)vr * p.NvS;
+  int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
+  if (rows > p.NvS) rows = p.NvS;
+  uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
+  const int nvec = p.H / 8;
+  const int64_t nwarps = (int64_t)gridDim.x * (EXPAND_THREADS / 32);
+  for (int64_t r = (int64_t)blockIdx.x * (EXPAND_THREADS / 32) + warp; r < rows; r += nwarps) {
+    int l = link[r];
+    if ((l & LINK_DUP_BIT) != 0) continue;
+    int next = l & LINK_NEXT_MASK;
+    const uint4* src = shard + (size_t)r * nvec;
+    for (int hop = 0; next != LINK_NONE && next < rows && hop < MAX_TOPK; ++hop) {
+      uint4* dstp = shard + (size_t)next * nvec;
+      int v = lane;
+      for (; v + 96 < nvec; v += 128) {
+        uint4 a = src[v], b = src[v + 32], c2 = src[v + 64], d = src[v + 96];
+        dstp[v] = a; dstp[v + 32] = b; dstp[v + 64] = c2; dstp[v + 96] = d;
+      }
+      for (; v < nvec; v += 32) dstp[v] = src[v];
+      next = link[next] & LINK_NEXT_MASK;
+    }
+  }
+}
+
+template <int ST>
+static int launch_dispatch_t(const BufferCtx& c, DispatchParams& p, size_t smem,
+                             cudaStream_t stream) {
+  static thread_local size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_dispatch_kernel<ST>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  dim3 grid(c.num_sms, c.Rv());
+  MEP_CUDA_OK(launch_coop((const void*)ep_dispatch_kernel<ST>, grid, dim3(DISPATCH_THREADS), smem,
+                          stream, p));
+  return 0;
+}
+
+}  // namespace mep
+
+using namespace mep;
+
+extern "C" {
+
+// x [Rv][S][H] bf16, w [Rv][S][K] fp32 or null, dst [Rv][N], zero_fill [Rv][2epn][2],
+// link_out [Rv][NvS] or null.  fresh != 0: the plan comes from the planner launch that
+// precedes this one on the stream (its barrier stands in for the entry sync).
+int mep_launch_dispatch(const void* ctx_, const void* x, const float* w, const int32_t* dst,
+                        const int32_t* zero_fill, int32_t* link_out, int entry_barrier, int fresh,
+                        cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  if (c.H % 8 != 0) return fail(-1, "dispatch needs H %% 8 == 0 (got %d)", c.H);
+  DispatchParams p;
+  p.sync = c.sync(KID_DISPATCH);
+  p.S = c.S; p.K = c.K; p.H = c.H; p.epn = c.epn;
+  p.N = c.N; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
+  p.weights_off = c.ml.weights_off; p.link_off = c.ml.link_off;
+  p.x = (const __nv_bfloat16*)x; p.w = w; p.dst = dst; p.zero_fill = zero_fill;
+  p.hidden = (__nv_bfloat16*)c.hidden; p.link_out = link_out;
+  p.entry_barrier = entry_barrier; p.fresh = fresh;
+  const size_t row = (size_t)c.H * 2;
+  // virtual groups must keep gridDim.x * R CTAs co-resident: leave room for 2 CTAs per SM
+  const size_t budget = c.virt ? 100 * 1024 : 200 * 1024;
+  if (9 * row <= budget) return launch_dispatch_t<8>(c, p, 9 * row, stream);
+  if (5 * row <= budget) return launch_dispatch_t<4>(c, p, 5 * row, stream);
+  if (3 * row <= 220 * 1024) return launch_dispatch_t<2>(c, p, 3 * row, stream);
+  return fail(-2, "dispatch: H=%d does not fit a 2-stage ring", c.H);
+}
+
+// Copy every primary row to its duplicates inside this rank's shard.
+int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_seqlens,
+                      cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  ExpandParams p;
+  p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
+  p.rank_base = c.virt ? 0 : c.rank;
+  p.hidden = (__nv_bfloat16*)c.hidden; p.link = link; p.cu_seqlens = cu_seqlens;
+  dim3 grid(c.num_sms_local, c.Rv());
+  ep_expand_kernel<<<grid, EXPAND_THREADS, 0, stream>>>(p);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

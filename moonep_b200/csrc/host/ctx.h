@@ -1,0 +1,64 @@
+// Host-side description of one Buffer: sizes, the symmetric buffers and the local scratch.
+// Created once (mep_ctx_create) and passed by handle to every launcher, like the `ctx` dict
+// the reference threads through its launch_* functions (moonep/api.py:200-414).
+//
+// virt != 0 marks a single-GPU virtual group: the "symmetric" buffers hold all R chunks on
+// this device, every per-rank local tensor is stacked [R, ...] contiguously, and every
+// kernel is launched with gridDim.y == R so that one cooperative launch runs all ranks.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "common/layout.h"
+#include "device/sync.cuh"
+
+namespace mep {
+
+struct BufferCtx {
+  int rank, R, virt;
+  int E, epn, S, K, H, token_padding, num_sms, num_sms_local;
+  int64_t N, NvS;
+  void* hidden;            // bf16 [R][hidden_stride_rows][H], symmetric
+  int64_t hidden_stride;   // rows between consecutive ranks' shards
+  int32_t* meta;           // int32 [R][meta_stride], symmetric
+  int64_t meta_stride;
+  MetaLayout ml;
+  int32_t* sync_state;     // [Rv][SYNC_STATE_INTS]
+  int32_t* status;         // host-visible [8]
+  int32_t* plan_scratch;   // [Rv][plan_scratch_ints]
+  int64_t plan_scratch_ints;
+  unsigned long long timeout_ns;
+  int sm_count;
+
+  int Rv() const { return virt ? R : 1; }
+  SyncCtx sync(int kernel_id) const {
+    SyncCtx s;
+    s.rank_base = virt ? 0 : rank;
+    s.R = R;
+    s.meta = meta;
+    s.meta_stride = meta_stride;
+    s.flags_off = ml.flags_off;
+    s.sync_state = sync_state;
+    s.status = status;
+    s.timeout_ns = timeout_ns;
+    s.kernel_id = kernel_id;
+    return s;
+  }
+};
+
+// Scratch ints per rank needed by the planner: tpe_cumsum[R*E] + alloc[E*R] +
+// alloc_cumsum[E*R] + expert_off[R*E] + per-CTA histograms [num_sms*E].
+inline int64_t plan_scratch_ints(int R, int E, int num_sms) {
+  return (int64_t)4 * R * E + (int64_t)num_sms * E;
+}
+
+// Cooperative launch helper: all CTAs of grid (gx, gy) must be co-resident.
+template <class Params>
+inline cudaError_t launch_coop(const void* kernel, dim3 grid, dim3 block, size_t smem,
+                               cudaStream_t stream, Params& params) {
+  void* args[] = {(void*)&params};
+  return cudaLaunchCooperativeKernel(kernel, grid, block, args, smem, stream);
+}
+
+}  // namespace mep
