@@ -1,0 +1,537 @@
+// Grouped bf16 GEMM for sm_100a on the 5th-generation tensor cores: tcgen05.mma issued by one
+// thread per CTA, operands staged in shared memory by tiled TMA loads (no cluster multicast),
+// fp32 accumulators in tensor memory, read back with tcgen05.ld for fused epilogues.
+//
+// The reference ships no GEMM: it hands cu_seqlens and the [2*epn, H, H'] compute view to the
+// host framework's "VM group GEMM" (README.md:45-68).  This kernel is that GEMM.  One
+// persistent CTA per SM walks a static tile list derived on the device from cu_seqlens (no
+// host synchronisation), with three warp roles:
+//   warp 0      TMA producer        (4-stage ring of 128x64 A and 256x64 B tiles, 48 KB each)
+//   warp 1      MMA issuer          (128x256x16 UMMAs, two 256-column TMEM accumulators)
+//   warps 2..5  epilogue            (TMEM -> registers -> global), overlapped with the next
+//                                   tile's main loop through the second accumulator
+// Modes:
+//   token-major (groups partition the rows of A and C):
+//        C[rows of g] = A[rows of g] * B[g]     B K-major ([N][K]) or MN-major ([K][N])
+//        epilogues: bf16 store, fp32 store, or SwiGLU: the tile holds 128 gate and 128 up
+//        columns of the same output columns; writes gate, up and silu(gate)*up*row_scale.
+//        Up to two K segments accumulate into one tile (dX = dG*Wg^T + dU*Wu^T).
+//   weight-grad (groups partition the REDUCTION dimension):
+//        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output.
+// Group g < split reads/writes allocation 0 (local experts), g >= split allocation 1 (this
+// rank's prefetch / reduce slots): the [2*epn] compute view never has to be contiguous.
+// Every mbarrier wait is bounded; on expiry the CTA records an error, drains and frees TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "device/tcgen05.cuh"
+#include "host/errors.h"
+
+namespace mep {
+void* driver_tensor_map_encode();
+
+constexpr int BM = 128, BN = 256, BK = 64, GEMM_STAGES = 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int MAX_GROUPS = 2048;
+constexpr int GEMM_SMEM = GEMM_STAGES * STAGE_BYTES + 1024;
+
+enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+
+struct GemmKParams {
+  CUtensorMap a[2];
+  CUtensorMap b[2][2];
+  const int32_t* cu_seqlens;
+  int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
+  void* out[3];
+  const float* row_scale;
+  long long ldc;
+  int32_t* status;
+  unsigned long long timeout_ns;
+};
+
+struct Tile {
+  int g, row0, rows, n0, num_kb, alloc, g_local, m0;
+  bool valid;
+};
+
+__device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volatile int* s_abort,
+                                          const GemmKParams& p, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255u) == 0) {
+      if (*s_abort) return false;
+      if (globaltimer_ns() - t0 > p.timeout_ns) {
+        *s_abort = 1;
+        if (p.status != nullptr && atomicCAS(p.status, 0, ST_TIMEOUT_MBAR) == 0) {
+          p.status[1] = KID_GEMM;
+          p.status[2] = where;
+          p.status[3] = (int)blockIdx.x;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+template <bool WGRAD, int EPI>
+__device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int* s_end,
+                                         const int* s_prefix, int n_tiles_n) {
+  Tile t;
+  t.valid = true;
+  if constexpr (WGRAD) {
+    const int mt = p.Mw / BM;
+    const int tpg = mt * n_tiles_n;
+    t.g = id / tpg;
+    int local = id - t.g * tpg;
+    int ni = local / mt, mi = local - ni * mt;
+    int start = t.g == 0 ? 0 : s_end[t.g - 1];
+    t.row0 = start;
+    t.rows = s_end[t.g] - start;
+    t.m0 = mi * BM;
+    t.n0 = ni * BN;
+    t.num_kb = (t.rows + BK - 1) / BK;
+    if (t.rows <= 0 && t.g >= p.zero_empty_below) t.valid = false;
+  } else {
+    // largest g with prefix[g] * n_tiles_n <= id
+    int lo = 0, hi = p.ngroups - 1;
+    while (lo < hi) {
+      int mid = (lo + hi + 1) >> 1;
+      if ((long long)s_prefix[mid] * n_tiles_n <= id) lo = mid; else hi = mid - 1;
+    }
+    t.g = lo;
+    int start = t.g == 0 ? 0 : s_end[t.g - 1];
+    int len = s_end[t.g] - start;
+    int mt = (len + BM - 1) / BM;
+    int local = id - s_prefix[t.g] * n_tiles_n;
+    int ni = local / mt, mi = local - ni * mt;
+    t.row0 = start + mi * BM;
+    t.rows = min(BM, s_end[t.g] - t.row0);
+    t.m0 = 0;
+    t.n0 = ni * (EPI == EPI_SWIGLU ? BN / 2 : BN);
+    t.num_kb = p.nseg * (p.K / BK);
+  }
+  t.alloc = t.g >= p.split ? 1 : 0;
+  t.g_local = t.alloc ? t.g - p.split : t.g;
+  return t;
+}
+
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t full[GEMM_STAGES];
+  __shared__ __align__(8) uint64_t empty[GEMM_STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_abort;
+  __shared__ int s_end[MAX_GROUPS];
+  __shared__ int s_prefix[MAX_GROUPS + 1];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+  volatile int* abortp = &s_abort;
+
+  if (tid == 0) {
+    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    mbar_fence_init();
+    s_abort = 0;
+  }
+  // group table
+  for (int g = tid; g < p.ngroups; g += GEMM_THREADS)
+    s_end[g] = p.cu_seqlens != nullptr ? p.cu_seqlens[g] : p.total_rows;
+  __syncthreads();
+  if (warp == 0) {
+    // exclusive prefix of M tiles per group (token-major); cheap serial-by-chunks scan
+    int run = 0;
+    for (int g0 = 0; g0 < p.ngroups; g0 += 32) {
+      int g = g0 + lane;
+      int len = 0;
+      if (g < p.ngroups) len = s_end[g] - (g == 0 ? 0 : s_end[g - 1]);
+      int mt = len > 0 ? (len + BM - 1) / BM : 0;
+      int incl = mt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (g < p.ngroups) s_prefix[g] = run + incl - mt;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_prefix[p.ngroups] = run;
+  }
+  if (warp == 1) {
+    tmem_alloc(&s_tmem, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem;
+
+  const int bn_eff = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  const int n_tiles_n = (p.N + bn_eff - 1) / bn_eff;
+  long long total_tiles;
+  if constexpr (WGRAD) total_tiles = (long long)p.ngroups * (p.Mw / BM) * n_tiles_n;
+  else total_tiles = (long long)s_prefix[p.ngroups] * n_tiles_n;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      tma_prefetch_desc(&p.a[0]);
+      tma_prefetch_desc(&p.b[0][0]);
+      int it = 0;
+      bool ok = true;
+      for (long long id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+        Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+        if (!t.valid) continue;
+        const int kb_per_seg = WGRAD ? t.num_kb : p.K / BK;
+        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+          const int s = it % GEMM_STAGES;
+          if (it >= GEMM_STAGES &&
+              !gemm_wait(&empty[s], ((uint32_t)(it / GEMM_STAGES) & 1u) ^ 1u, abortp, p, 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          const int seg = kb / kb_per_seg;
+          const int k0 = (kb - seg * kb_per_seg) * BK;
+          if constexpr (WGRAD) {
+            // A: [token rows][Mw cols], two 64-column blocks; B: [token rows][N cols], four
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &p.a[0], t.m0 + 64 * j, t.row0 + k0, &full[s]);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &p.b[0][0], t.n0 + 64 * j, t.row0 + k0, &full[s]);
+          } else {
+            tma_load_2d(sa, &p.a[seg], k0, t.row0, &full[s]);
+            const int erow = t.g_local * p.rows_per_expert;
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                if constexpr (EPI == EPI_SWIGLU) {
+                  const int part = j / (BN / 128);
+                  tma_load_2d(sb + j * 8192, &p.b[part][t.alloc],
+                              t.n0 + 64 * (j % (BN / 128)), erow + k0, &full[s]);
+                } else {
+                  tma_load_2d(sb + j * 8192, &p.b[seg][t.alloc], t.n0 + 64 * j, erow + k0, &full[s]);
+                }
+              }
+            } else {
+              tma_load_2d(sb, &p.b[seg][t.alloc], k0, erow + t.n0, &full[s]);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_instr_desc_bf16(BM, BN, A_MN, B_MN);
+      int it = 0, tile_n = 0;
+      bool ok = true;
+      for (long long id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
+        Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+        if (!t.valid) continue;
+        const int acc = tile_n & 1;
+        if (tile_n >= 2 &&
+            !gemm_wait(&acc_empty[acc], ((uint32_t)(tile_n >> 1) & 1u) ^ 1u, abortp, p, 2)) break;
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+          const int s = it % GEMM_STAGES;
+          if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint32_t sb = sa + A_TILE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sb + kk * 32, 16, 1024);
+            umma_bf16(tacc, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);       // stage reusable once these MMAs have read it
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);    // accumulator complete
+        ++tile_n;
+      }
+    }
+  } else {
+    // ================= epilogue (4 warps, one TMEM lane quarter each) =================
+    const int q = warp & 3;
+    const int r_in_tile = q * 32 + lane;
+    int tile_n = 0;
+    for (long long id = blockIdx.x; id < total_tiles; id += gridDim.x) {
+      Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+      if (!t.valid) continue;
+      const int acc = tile_n & 1;
+      if (!gemm_wait(&acc_full[acc], (uint32_t)(tile_n >> 1) & 1u, abortp, p, 4)) break;
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + (uint32_t)acc * BN + ((uint32_t)(q * 32) << 16);
+      const bool have_acc = t.num_kb > 0;
+      if constexpr (EPI == EPI_SWIGLU) {
+        const bool row_ok = r_in_tile < t.rows;
+        const long long row = (long long)t.row0 + r_in_tile;
+        const float rs = (row_ok && p.row_scale != nullptr) ? p.row_scale[row] : 1.f;
+        __nv_bfloat16* og = (__nv_bfloat16*)p.out[0];
+        __nv_bfloat16* ou = (__nv_bfloat16*)p.out[1];
+        __nv_bfloat16* oa = (__nv_bfloat16*)p.out[2];
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(tacc + c * 32, rg);
+          tmem_ld_32x32(tacc + 128 + c * 32, ru);
+          tmem_ld_wait();
+          const int col = t.n0 + c * 32;
+          if (row_ok && col < p.N) {
+            uint32_t pg[16], pu[16], pa[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float g0 = __uint_as_float(rg[2 * i]), g1 = __uint_as_float(rg[2 * i + 1]);
+              float u0 = __uint_as_float(ru[2 * i]), u1 = __uint_as_float(ru[2 * i + 1]);
+              __nv_bfloat162 hg = __floats2bfloat162_rn(g0, g1);
+              __nv_bfloat162 hu = __floats2bfloat162_rn(u0, u1);
+              // the saved gate/up are bf16; the activation is computed from the rounded values
+              // so that backward recomputes exactly what forward used
+              float2 fg = __bfloat1622float2(hg), fu = __bfloat1622float2(hu);
+              float a0 = fg.x / (1.f + __expf(-fg.x)) * fu.x * rs;
+              float a1 = fg.y / (1.f + __expf(-fg.y)) * fu.y * rs;
+              __nv_bfloat162 ha = __floats2bfloat162_rn(a0, a1);
+              pg[i] = *reinterpret_cast<uint32_t*>(&hg);
+              pu[i] = *reinterpret_cast<uint32_t*>(&hu);
+              pa[i] = *reinterpret_cast<uint32_t*>(&ha);
+            }
+            const long long off = row * p.ldc + col;
+            if (col + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (og) reinterpret_cast<uint4*>(og + off)[v] = make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
+                if (ou) reinterpret_cast<uint4*>(ou + off)[v] = make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+                reinterpret_cast<uint4*>(oa + off)[v] = make_uint4(pa[4 * v], pa[4 * v + 1], pa[4 * v + 2], pa[4 * v + 3]);
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < p.N; ++i) {
+                const __nv_bfloat16* sg = reinterpret_cast<const __nv_bfloat16*>(pg);
+                const __nv_bfloat16* su = reinterpret_cast<const __nv_bfloat16*>(pu);
+                const __nv_bfloat16* sa2 = reinterpret_cast<const __nv_bfloat16*>(pa);
+                if (og) og[off + i] = sg[i];
+                if (ou) ou[off + i] = su[i];
+                oa[off + i] = sa2[i];
+              }
+            }
+          }
+        }
+      } else {
+        bool row_ok;
+        long long off_row;
+        int col_base;
+        if constexpr (WGRAD) {
+          row_ok = t.m0 + r_in_tile < p.Mw;
+          off_row = ((long long)t.g_local * p.Mw + t.m0 + r_in_tile) * p.ldc;
+          col_base = t.n0;
+        } else {
+          row_ok = r_in_tile < t.rows;
+          off_row = ((long long)t.row0 + r_in_tile) * p.ldc;
+          col_base = t.n0;
+        }
+        void* outp = WGRAD ? p.out[t.alloc] : p.out[0];
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld_32x32(tacc + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const int col = col_base + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          if constexpr (EPI == EPI_F32) {
+            float* o = (float*)outp + off_row + col;
+            if (col + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (p.accumulate) {
+                  float4 y = reinterpret_cast<float4*>(o)[v];
+                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+                }
+                reinterpret_cast<float4*>(o)[v] = x;
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < p.N; ++i)
+                o[i] = __uint_as_float(r[i]) + (p.accumulate ? o[i] : 0.f);
+            }
+          } else {
+            __nv_bfloat16* o = (__nv_bfloat16*)outp + off_row + col;
+            uint32_t pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+              pk[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            if (col + 32 <= p.N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v)
+                reinterpret_cast<uint4*>(o)[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+            } else {
+              const __nv_bfloat16* sp = reinterpret_cast<const __nv_bfloat16*>(pk);
+              for (int i = 0; i < 32 && col + i < p.N; ++i) o[i] = sp[i];
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      ++tile_n;
+    }
+  }
+  // ---- teardown: everything joins, in-flight work is given time to land on an abort ----------
+  tc_fence_before();
+  __syncthreads();
+  if (s_abort) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) { }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+struct GemmDesc {
+  int32_t mode, epi, b_mn, nseg;
+  int32_t ngroups, split, total_rows, N, K, rows_per_expert, Mw, accumulate, zero_empty_below, grid;
+  int64_t a_rows;
+  int64_t lda[2];
+  const void* a[2];
+  const void* b[2][2];
+  int64_t b_rows[2];
+  int64_t ldb;
+  const int32_t* cu_seqlens;
+  void* out[3];
+  int64_t ldc;
+  const float* row_scale;
+  int32_t* status;
+  int64_t timeout_ns;
+};
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                             const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                             CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                             CUtensorMapFloatOOBfill);
+
+// 2-D bf16 tensor [rows][cols] (row stride ld elements), box [box_rows][box_cols], 128B swizzle.
+static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld,
+                    int box_cols, int box_rows) {
+  EncodeFn enc = (EncodeFn)driver_tensor_map_encode();
+  if (!enc) return fail(-10, "CUDA driver entry cuTensorMapEncodeTiled not available");
+  if (((uintptr_t)base & 15) != 0 || (ld * 2) % 16 != 0)
+    return fail(-11, "GEMM operand must be 16-byte aligned with a 16-byte multiple row stride");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-12, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(kp);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace mep
+
+using namespace mep;
+
+extern "C" {
+
+int mep_gemm_desc_bytes() { return (int)sizeof(GemmDesc); }
+
+int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
+  if (d->ngroups < 1 || d->ngroups > MAX_GROUPS) return fail(-1, "gemm: ngroups=%d out of range", d->ngroups);
+  GemmKParams kp;
+  std::memset(&kp, 0, sizeof(kp));
+  kp.cu_seqlens = d->cu_seqlens; kp.ngroups = d->ngroups; kp.split = d->split;
+  kp.total_rows = d->total_rows; kp.N = d->N; kp.K = d->K; kp.nseg = d->nseg;
+  kp.rows_per_expert = d->rows_per_expert; kp.Mw = d->Mw; kp.accumulate = d->accumulate;
+  kp.zero_empty_below = d->zero_empty_below;
+  kp.out[0] = d->out[0]; kp.out[1] = d->out[1]; kp.out[2] = d->out[2];
+  kp.row_scale = d->row_scale; kp.ldc = d->ldc; kp.status = d->status;
+  kp.timeout_ns = (unsigned long long)(d->timeout_ns > 0 ? d->timeout_ns : 2000000000ll);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = d->grid > 0 ? d->grid : sms;
+  int rc = 0;
+  if (d->mode == 1) {
+    // weight grad: A [a_rows][Mw] and B [a_rows][N], both read as MN-major 64x64 boxes
+    if (d->Mw % BM != 0) return fail(-2, "wgrad: Mw=%d must be a multiple of %d", d->Mw, BM);
+    if ((rc = make_map(&kp.a[0], d->a[0], d->a_rows, d->Mw, d->lda[0], 64, BK))) return rc;
+    if ((rc = make_map(&kp.b[0][0], d->b[0][0], d->a_rows, d->N, d->ldb, 64, BK))) return rc;
+    kp.a[1] = kp.a[0]; kp.b[0][1] = kp.b[1][0] = kp.b[1][1] = kp.b[0][0];
+    if (d->epi != EPI_F32) return fail(-3, "wgrad writes fp32");
+    return launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
+  }
+  if (d->K % BK != 0) return fail(-4, "gemm: K=%d must be a multiple of %d", d->K, BK);
+  if (d->nseg < 1 || d->nseg > 2) return fail(-5, "gemm: nseg=%d", d->nseg);
+  for (int s = 0; s < d->nseg; ++s)
+    if ((rc = make_map(&kp.a[s], d->a[s], d->a_rows, d->K, d->lda[s], BK, BM))) return rc;
+  if (d->nseg == 1) kp.a[1] = kp.a[0];
+  const int nsel = (d->epi == EPI_SWIGLU) ? 2 : d->nseg;
+  for (int s = 0; s < 2; ++s)
+    for (int al = 0; al < 2; ++al) {
+      const void* base = d->b[s < nsel ? s : 0][al] ? d->b[s < nsel ? s : 0][al] : d->b[s < nsel ? s : 0][0];
+      const int64_t rows = d->b[s < nsel ? s : 0][al] ? d->b_rows[al] : d->b_rows[0];
+      if (d->b_mn) {   // [K rows][N cols] per expert
+        if ((rc = make_map(&kp.b[s][al], base, rows, d->N, d->ldb, 64, BK))) return rc;
+      } else {         // [N rows][K cols] per expert
+        if ((rc = make_map(&kp.b[s][al], base, rows, d->K, d->ldb, BK, BN))) return rc;
+      }
+    }
+  if (d->epi == EPI_SWIGLU) {
+    if (!d->b_mn) return fail(-6, "swiglu epilogue expects MN-major weights");
+    return launch_gemm<false, false, true, EPI_SWIGLU>(kp, grid, stream);
+  }
+  if (d->epi == EPI_BF16)
+    return d->b_mn ? launch_gemm<false, false, true, EPI_BF16>(kp, grid, stream)
+                   : launch_gemm<false, false, false, EPI_BF16>(kp, grid, stream);
+  if (d->epi == EPI_F32)
+    return d->b_mn ? launch_gemm<false, false, true, EPI_F32>(kp, grid, stream)
+                   : launch_gemm<false, false, false, EPI_F32>(kp, grid, stream);
+  return fail(-7, "gemm: unknown epilogue %d", d->epi);
+}
+
+}  // extern "C"

@@ -1,0 +1,226 @@
+"""Python front end of the tcgen05 grouped GEMM (``csrc/device/grouped_gemm.cu``).
+
+The reference has no GEMM; it leaves the ``[2*epn, H, H']`` "VM group GEMM" to the host
+framework (README.md:45-68).  These wrappers are that GEMM for the expert FFN of the MoE layer:
+
+========================  ==========================  =======================================
+op                        math                        operands
+========================  ==========================  =======================================
+``gateup_swiglu``         act = silu(x Wg)*(x Wu)*w   x [rows,H] . Wg/Wu [G,H,H'] (MN-major B)
+``down``                  y = act Wd^T                act [rows,H'] . Wd [G,H,H'] (K-major B)
+``down_dgrad``            dact = dy Wd                dy [rows,H] . Wd [G,H,H'] (MN-major B)
+``gateup_dgrad``          dx = dg Wg^T + du Wu^T      two K segments, K-major B
+``wgrad``                 dW[g] (+)= a_g^T b_g        a [rows,H], b [rows,H'] -> fp32 [G,H,H']
+``dense``                 c = a b                     one group (router logits)
+========================  ==========================  =======================================
+
+Groups are the VM groups of ``cu_seqlens``; ``*_slot`` tensors are this rank's prefetch / reduce
+slots and serve groups ``>= split`` (they may be ``None`` when the plan never uses them).
+Requirements: bf16 operands, 16-byte aligned, reduction length a multiple of 64, group sizes a
+multiple of 64 for ``wgrad``.  Every call raises if the native library is missing; there is no
+eager fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _native as nat
+from .._native import I, P
+
+EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
+
+
+class _GemmDesc(ctypes.Structure):
+    _fields_ = [
+        ("mode", ctypes.c_int32), ("epi", ctypes.c_int32), ("b_mn", ctypes.c_int32),
+        ("nseg", ctypes.c_int32), ("ngroups", ctypes.c_int32), ("split", ctypes.c_int32),
+        ("total_rows", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
+        ("rows_per_expert", ctypes.c_int32), ("Mw", ctypes.c_int32),
+        ("accumulate", ctypes.c_int32), ("zero_empty_below", ctypes.c_int32),
+        ("grid", ctypes.c_int32),
+        ("a_rows", ctypes.c_int64), ("lda", ctypes.c_int64 * 2), ("a", ctypes.c_void_p * 2),
+        ("b", (ctypes.c_void_p * 2) * 2), ("b_rows", ctypes.c_int64 * 2), ("ldb", ctypes.c_int64),
+        ("cu_seqlens", ctypes.c_void_p), ("out", ctypes.c_void_p * 3), ("ldc", ctypes.c_int64),
+        ("row_scale", ctypes.c_void_p), ("status", ctypes.c_void_p), ("timeout_ns", ctypes.c_int64),
+    ]
+
+
+nat.declare("mep_gemm_desc_bytes", I, [])
+nat.declare("mep_gemm_launch", I, [ctypes.POINTER(_GemmDesc), P])
+
+_status: dict[int, torch.Tensor] = {}
+_checked_layout = False
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32[8] that GEMM kernels flag on a bounded-wait expiry (0 = healthy)."""
+    idx = torch.device(device).index or 0
+    if idx not in _status:
+        _status[idx] = torch.zeros(8, dtype=torch.int32, device=f"cuda:{idx}")
+    return _status[idx]
+
+
+def check_status(device="cuda") -> None:
+    st = status_word(device).tolist()
+    if st[0] != 0:
+        raise RuntimeError(f"grouped GEMM: bounded wait expired (code {st[0]}, where {st[2]}, CTA {st[3]})")
+
+
+def _launch(d: _GemmDesc) -> None:
+    global _checked_layout
+    if not _checked_layout:
+        assert nat.call("mep_gemm_desc_bytes") == ctypes.sizeof(_GemmDesc), "GemmDesc layout mismatch"
+        _checked_layout = True
+    rc = nat.call("mep_gemm_launch", ctypes.byref(d), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"grouped GEMM launch failed: {nat.last_error()} (code {rc})")
+
+
+def _bf16(t: torch.Tensor, name: str) -> torch.Tensor:
+    assert t.is_cuda and t.dtype == torch.bfloat16, f"{name} must be a CUDA bf16 tensor"
+    assert t.stride(-1) == 1 and t.data_ptr() % 16 == 0, f"{name} must be dense and 16-byte aligned"
+    return t
+
+
+def _groups(cu_seqlens, rows):
+    if cu_seqlens is None:
+        return None, 1
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.is_cuda and cu_seqlens.is_contiguous()
+    return cu_seqlens.data_ptr(), cu_seqlens.numel()
+
+
+def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_expert, b_mn, epi,
+                 outs, ldc, row_scale=None, total_rows=None, grid=0):
+    d = _GemmDesc()
+    d.mode, d.epi, d.b_mn, d.nseg = 0, epi, int(b_mn), len(a_segs)
+    cu_ptr, ngroups = _groups(cu_seqlens, None)
+    d.ngroups = ngroups
+    d.split = ngroups if split is None else split
+    a0 = a_segs[0]
+    d.total_rows = a0.shape[0] if total_rows is None else total_rows
+    d.N, d.K, d.rows_per_expert, d.Mw = N, K, rows_per_expert, 0
+    d.grid = grid
+    d.a_rows = a0.shape[0]
+    for i, a in enumerate(a_segs):
+        _bf16(a, "A")
+        assert a.shape == a0.shape and a.shape[1] == K
+        d.a[i] = a.data_ptr()
+        d.lda[i] = a.stride(0)
+    ld = None
+    for i, (b, bs) in enumerate(zip(b_sel, b_slot_sel)):
+        _bf16(b, "B")
+        assert b.is_contiguous()
+        d.b[i][0] = b.data_ptr()
+        d.b_rows[0] = b.shape[0] * b.shape[1]
+        ld = b.shape[2]
+        if bs is not None:
+            _bf16(bs, "B slots")
+            assert bs.is_contiguous() and bs.shape[1:] == b.shape[1:]
+            d.b[i][1] = bs.data_ptr()
+            d.b_rows[1] = bs.shape[0] * bs.shape[1]
+        else:
+            d.b[i][1] = None
+            assert d.split >= ngroups, "groups >= split need slot weights"
+    d.ldb = ld
+    d.cu_seqlens = cu_ptr
+    for i, o in enumerate(outs):
+        d.out[i] = None if o is None else o.data_ptr()
+    d.ldc = ldc
+    d.row_scale = None if row_scale is None else row_scale.data_ptr()
+    d.status = status_word(a0.device).data_ptr()
+    _launch(d)
+
+
+def gateup_swiglu(x, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None,
+                  row_scale=None, save_gate_up=True):
+    """``act[rows,H'] = silu(x Wg[g]) * (x Wu[g]) * row_scale``; also returns bf16 gate / up.
+
+    ``x`` [rows, H]; ``wg``/``wu`` [G0, H, H'] (+ optional slot tensors for groups >= split)."""
+    rows, H = x.shape
+    Hp = wg.shape[2]
+    assert wg.shape[1] == H and wu.shape == wg.shape
+    act = torch.empty(rows, Hp, dtype=torch.bfloat16, device=x.device)
+    gate = torch.empty_like(act) if save_gate_up else None
+    up = torch.empty_like(act) if save_gate_up else None
+    if row_scale is not None:
+        assert row_scale.dtype == torch.float32 and row_scale.numel() >= rows
+    _tokens_gemm([x], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, Hp, H, H, True, EPI_SWIGLU,
+                 [gate, up, act], Hp, row_scale)
+    return act, gate, up
+
+
+def down(act, wd, cu_seqlens, *, wd_slot=None, split=None, out=None):
+    """``y[rows,H] = act[rows,H'] Wd[g]^T`` with ``wd`` [G0, H, H']."""
+    rows, Hp = act.shape
+    H = wd.shape[1]
+    assert wd.shape[2] == Hp
+    y = torch.empty(rows, H, dtype=torch.bfloat16, device=act.device) if out is None else out
+    _tokens_gemm([act], [wd], [wd_slot], cu_seqlens, split, H, Hp, H, False, EPI_BF16, [y], y.stride(0))
+    return y
+
+
+def down_dgrad(dy, wd, cu_seqlens, *, wd_slot=None, split=None):
+    """``dact[rows,H'] = dy[rows,H] Wd[g]``."""
+    rows, H = dy.shape
+    Hp = wd.shape[2]
+    out = torch.empty(rows, Hp, dtype=torch.bfloat16, device=dy.device)
+    _tokens_gemm([dy], [wd], [wd_slot], cu_seqlens, split, Hp, H, H, True, EPI_BF16, [out], Hp)
+    return out
+
+
+def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None, out=None):
+    """``dx[rows,H] = dg Wg[g]^T + du Wu[g]^T`` (two K segments into one accumulator)."""
+    rows, Hp = dg.shape
+    H = wg.shape[1]
+    dx = torch.empty(rows, H, dtype=torch.bfloat16, device=dg.device) if out is None else out
+    _tokens_gemm([dg, du], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, H, Hp, H, False,
+                 EPI_BF16, [dx], dx.stride(0))
+    return dx
+
+
+def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False):
+    """``grad[g] (+)= a[rows of g]^T b[rows of g]``; ``a`` [rows, M], ``b`` [rows, N], fp32 grads
+    ``[G0, M, N]`` (+ slot grads for groups >= split).  Group sizes must be multiples of 64
+    (padding rows must be zero in ``a`` or ``b``).  Empty groups below ``split`` are zeroed
+    unless ``accumulate``; empty slot groups are left untouched."""
+    _bf16(a, "a"), _bf16(b, "b")
+    rows, M = a.shape
+    N = b.shape[1]
+    assert b.shape[0] == rows and grad_local.dtype == torch.float32 and grad_local.is_contiguous()
+    assert grad_local.shape[1:] == (M, N)
+    d = _GemmDesc()
+    d.mode, d.epi, d.b_mn, d.nseg = 1, EPI_F32, 1, 1
+    cu_ptr, ngroups = _groups(cu_seqlens, rows)
+    d.ngroups = ngroups
+    d.split = ngroups if split is None else split
+    d.total_rows, d.N, d.K, d.rows_per_expert, d.Mw = rows, N, 0, 0, M
+    d.accumulate = int(accumulate)
+    d.zero_empty_below = 0 if accumulate else d.split
+    d.a_rows = rows
+    d.a[0], d.lda[0] = a.data_ptr(), a.stride(0)
+    d.b[0][0], d.ldb = b.data_ptr(), b.stride(0)
+    d.cu_seqlens = cu_ptr
+    d.out[0] = grad_local.data_ptr()
+    if grad_slot is not None:
+        assert grad_slot.dtype == torch.float32 and grad_slot.is_contiguous()
+        d.out[1] = grad_slot.data_ptr()
+    else:
+        assert d.split >= ngroups
+    d.ldc = N
+    d.status = status_word(a.device).data_ptr()
+    _launch(d)
+    return grad_local
+
+
+def dense(a, b, *, out_dtype=torch.float32, b_is_kn=True):
+    """``c[M,N] = a[M,K] b`` with ``b`` [K,N] (``b_is_kn``) or [N,K]; one group."""
+    M, K = a.shape
+    N = b.shape[1] if b_is_kn else b.shape[0]
+    out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    epi = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
+    _tokens_gemm([a], [b[None]], [None], None, None, N, K, b.shape[0], b_is_kn, epi, [out], N,
+                 total_rows=M)
+    return out

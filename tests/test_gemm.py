@@ -1,0 +1,119 @@
+"""tcgen05 grouped GEMM against plain PyTorch fp32 references of the same ops."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(rows_per_group, dev="cuda"):
+    ends = torch.tensor(rows_per_group).cumsum(0).to(torch.int32).to(dev)
+    return ends, int(ends[-1])
+
+
+def _ref_tokens(a, w_all, ends, fn):
+    out = []
+    start = 0
+    for g, e in enumerate(ends.tolist()):
+        if e > start:
+            out.append(fn(a[start:e].float(), w_all[g].float()))
+        start = e
+    return torch.cat(out)
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    from moonep_b200.ops import gemm
+    torch.cuda.synchronize()
+    gemm.check_status()
+
+
+def _close(x, ref, tol=2e-2):
+    scale = float(ref.abs().max()) + 1e-6
+    err = float((x.float() - ref).abs().max()) / scale
+    assert err < tol, f"relative max error {err}"
+
+
+@pytest.mark.parametrize("groups", [[128, 256, 0, 128], [100, 0, 300, 1, 129, 64]])
+@pytest.mark.parametrize("H,Hp", [(256, 384), (512, 128)])
+def test_down_and_dgrads(groups, H, Hp):
+    from moonep_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(0)
+    ends, rows = _mk(groups)
+    G = len(groups)
+    split = G // 2
+    w_all = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.05).bfloat16()
+    w_loc, w_slot = w_all[:split].contiguous(), w_all[split:].contiguous()
+    act = torch.randn(rows, Hp, device="cuda", generator=g).bfloat16()
+    y = gemm.down(act, w_loc, ends, wd_slot=w_slot, split=split)
+    _close(y, _ref_tokens(act, w_all, ends, lambda a, w: a @ w.t()))
+    dy = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    dact = gemm.down_dgrad(dy, w_loc, ends, wd_slot=w_slot, split=split)
+    _close(dact, _ref_tokens(dy, w_all, ends, lambda a, w: a @ w))
+    wu_all = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.05).bfloat16()
+    dg = torch.randn(rows, Hp, device="cuda", generator=g).bfloat16()
+    du = torch.randn(rows, Hp, device="cuda", generator=g).bfloat16()
+    dx = gemm.gateup_dgrad(dg, du, w_loc, wu_all[:split].contiguous(), ends, wg_slot=w_slot,
+                           wu_slot=wu_all[split:].contiguous(), split=split)
+    ref = _ref_tokens(dg, w_all, ends, lambda a, w: a @ w.t()) + \
+        _ref_tokens(du, wu_all, ends, lambda a, w: a @ w.t())
+    _close(dx, ref)
+
+
+@pytest.mark.parametrize("groups", [[128, 256, 0, 128], [100, 0, 300, 1, 129, 64]])
+def test_gateup_swiglu(groups):
+    from moonep_b200.ops import gemm
+    H, Hp = 256, 384
+    g = torch.Generator(device="cuda").manual_seed(1)
+    ends, rows = _mk(groups)
+    G = len(groups)
+    wg = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.08).bfloat16()
+    wu = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.08).bfloat16()
+    x = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+    rs = torch.rand(rows, device="cuda", generator=g) + 0.5
+    act, gate, up = gemm.gateup_swiglu(x, wg, wu, ends, row_scale=rs)
+    g_ref = _ref_tokens(x, wg, ends, lambda a, w: a @ w)
+    u_ref = _ref_tokens(x, wu, ends, lambda a, w: a @ w)
+    _close(gate, g_ref)
+    _close(up, u_ref)
+    gb, ub = gate.float(), up.float()
+    a_ref = torch.nn.functional.silu(gb) * ub * rs[:, None]
+    _close(act, a_ref, tol=1e-2)
+
+
+@pytest.mark.parametrize("groups", [[128, 256, 0, 64], [64, 0, 0, 192, 320, 64]])
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_wgrad(groups, accumulate):
+    from moonep_b200.ops import gemm
+    M, N = 256, 320
+    g = torch.Generator(device="cuda").manual_seed(2)
+    ends, rows = _mk(groups)
+    G = len(groups)
+    split = G // 2
+    a = torch.randn(rows, M, device="cuda", generator=g).bfloat16()
+    b = torch.randn(rows, N, device="cuda", generator=g).bfloat16()
+    gl = torch.randn(split, M, N, device="cuda", generator=g)
+    gs = torch.randn(G - split, M, N, device="cuda", generator=g)
+    gl0, gs0 = gl.clone(), gs.clone()
+    gemm.wgrad(a, b, ends, gl, grad_slot=gs, split=split, accumulate=accumulate)
+    start = 0
+    for gi, e in enumerate(ends.tolist()):
+        ref = a[start:e].float().t() @ b[start:e].float()
+        tgt, base = (gl[gi], gl0[gi]) if gi < split else (gs[gi - split], gs0[gi - split])
+        if accumulate:
+            ref = ref + base
+        elif e == start and gi >= split:
+            ref = base                      # empty slot groups are left untouched
+        _close(tgt, ref, tol=1e-2)
+        start = e
+
+
+def test_dense_router_logits():
+    from moonep_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(300, 512, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(512, 64, device="cuda", generator=g) * 0.1).bfloat16()
+    c = gemm.dense(a, b)
+    _close(c, a.float() @ b.float(), tol=5e-3)
+    c2 = gemm.dense(a, b.t().contiguous(), b_is_kn=False, out_dtype=torch.bfloat16)
+    _close(c2, a.float() @ b.float())
