@@ -54,8 +54,17 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+# Number of native calls that launch at least one of this library's kernels (benchmarks read and
+# reset it to report how many launches a step takes).
+LAUNCHES = 0
+_LAUNCH_PREFIXES = ("mep_launch_", "mep_gemm_launch", "mep_router_", "mep_swiglu_", "mep_sgd_")
+
+
 def call(name: str, *args):
     """Call a declared entry point; raises if the symbol is missing (no silent fallback)."""
+    global LAUNCHES
+    if name.startswith(_LAUNCH_PREFIXES):
+        LAUNCHES += 1
     handle = lib()
     try:
         fn = getattr(handle, name)

@@ -115,11 +115,14 @@ class Buffer:
             assert num_sms * R * 1 <= 2 * props.multi_processor_count, \
                 "virtual group: num_sms * R CTAs must be co-resident (<= 2 per SM)"
         else:
-            assert dist.is_initialized(), "construct Buffer after init_process_group"
-            self.group = group if group is not None else dist.group.WORLD
-            assert dist.get_world_size(self.group) == R, \
-                f"num_ep_ranks={R} != group world size {dist.get_world_size(self.group)}"
-            self.rank = dist.get_rank(self.group)
+            if R == 1 and not dist.is_initialized():
+                self.group, self.rank = None, 0      # a lone rank needs no process group
+            else:
+                assert dist.is_initialized(), "construct Buffer after init_process_group"
+                self.group = group if group is not None else dist.group.WORLD
+                assert dist.get_world_size(self.group) == R, \
+                    f"num_ep_ranks={R} != group world size {dist.get_world_size(self.group)}"
+                self.rank = dist.get_rank(self.group)
             num_sms = 32 if num_sms is None else num_sms
             assert num_sms <= props.multi_processor_count
         self.num_sms = int(num_sms)
@@ -134,7 +137,8 @@ class Buffer:
 
         # ---- symmetric buffers ----------------------------------------------------------
         meta_ints = int(nat.call("mep_meta_chunk_ints", self.NvS, R, E))
-        if self.virtual:
+        self._solo = self.virtual or R == 1
+        if self._solo:
             self.hidden_buf = symm.create_local_group_tensor((self.NvS, H), torch.bfloat16, R, self.device)
             self.meta_buf = symm.create_local_group_tensor((meta_ints,), torch.int32, R, self.device)
             self.meta_mc = None
@@ -153,7 +157,7 @@ class Buffer:
         else:
             self.meta_buf[self.rank * self.meta_stride:(self.rank + 1) * self.meta_stride].zero_()
         torch.cuda.synchronize()
-        if not self.virtual:
+        if not self._solo:
             dist.barrier(group=self.group)
 
         # ---- local state ------------------------------------------------------------------
@@ -229,14 +233,14 @@ class Buffer:
         ``CommTimeoutError`` (epochs of different ranks may have diverged)."""
         self._require()
         torch.cuda.synchronize(self.device)
-        if not self.virtual:
+        if not self._solo:
             dist.barrier(group=self.group)
         self.status.zero_()
         self.sync_state.zero_()
         rows = self._meta_rows()
         rows[:, self.flags_off: self.flags_off + self.R].zero_()
         torch.cuda.synchronize(self.device)
-        if not self.virtual:
+        if not self._solo:
             dist.barrier(group=self.group)
 
     def _maybe_check(self):
@@ -532,7 +536,7 @@ class Buffer:
         try:
             self.comm_stream.synchronize()
             torch.cuda.synchronize(self.device)
-            if not self.virtual and dist.is_initialized():
+            if not self._solo and dist.is_initialized():
                 dist.barrier(group=self.group)
         finally:
             nat.call("mep_ctx_destroy", self._ctx)

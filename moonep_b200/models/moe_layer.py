@@ -1,0 +1,182 @@
+"""Expert-parallel MoE layer (router -> dispatch -> SwiGLU experts -> combine) with a full
+backward pass and an SGD step, built on ``Buffer`` and the tcgen05 grouped GEMM.
+
+The reference stops at the communication API and describes the integration in prose
+(README.md:43-156): the framework owns a ``[2*epn, H, H']`` compute view per projection (local
+experts followed by this rank's prefetch slots), runs its grouped GEMM over the VM groups of
+``cu_seqlens``, accumulates prefetch-slot weight grads in ``[R, epn, H, H']`` reduce buffers and
+calls ``reduce_grad``.  This module is that integration:
+
+forward   logits = x Wr -> top-k/softmax/histogram -> ``dispatch`` (fresh plan) ->
+          ``prefetch_weight`` -> gate/up GEMM with fused SwiGLU x route weight -> down GEMM
+          written straight into the Buffer's shard -> ``combine`` (zero copy)
+backward  ``dispatch(plan=...)`` of dy -> down dgrad / wgrad -> SwiGLU backward (also yields the
+          route-weight grads) -> gate/up wgrad and dgrad (into the shard) -> ``combine`` with the
+          weight-gather path (returns d route weights as [S, K]) -> ``reduce_grad`` -> router
+          backward.
+
+Weights are bf16, weight grads fp32 ("main grads"), written by the GEMM epilogues.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import buffer as symm
+from ..api import Buffer
+from ..ops import elementwise as ew
+from ..ops import gemm
+
+
+class ExpertPools:
+    """Process-global prefetch (bf16) and reduce (fp32) pools, ``[R, epn, H, H']`` each, mapped on
+    every rank.  Shared by all MoE layers of a model (README.md:56-58).  ``None`` when R == 1."""
+
+    def __init__(self, R: int, epn: int, H: int, Hp: int, group=None, rank: int = 0,
+                 train: bool = True):
+        self.R, self.epn, self.rank = R, epn, rank
+        self.names = ("gate", "up", "down")
+        self.prefetch = {}
+        self.reduce = {}
+        if R == 1:
+            return
+        for n in self.names:
+            t = symm.create_nvl_dist_tensor((epn, H, Hp), torch.bfloat16, group)
+            self.prefetch[n] = t.view(R, t.shape[0] // R, H, Hp)[:, :epn]
+            if train:
+                g = symm.create_nvl_dist_tensor((epn, H, Hp), torch.float32, group)
+                gv = g.view(R, g.shape[0] // R, H, Hp)[:, :epn]
+                gv[rank].zero_()
+                self.reduce[n] = gv
+        torch.cuda.synchronize()
+        dist.barrier(group=group)
+
+    def slot(self, name):
+        return self.prefetch[name][self.rank] if self.prefetch else None
+
+    def grad_slot(self, name):
+        return self.reduce[name][self.rank] if self.reduce else None
+
+
+class _MoEFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, layer):
+        buf: Buffer = layer.buf
+        epn = buf.epn
+        logits = gemm.dense(x, layer.w_router)                         # [S, E] fp32
+        topk, w, tpe = ew.router_topk(logits, buf.K, layer.router_bias)
+        hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
+        pools = layer.pools
+        if pools is not None and pools.prefetch:
+            ev = buf.prefetch_weight(
+                plan, async_finish=True, local_gate_weight=layer.w_gate,
+                local_up_weight=layer.w_up, local_down_weight=layer.w_down,
+                gate_prefetch_buffer=pools.prefetch["gate"], up_prefetch_buffer=pools.prefetch["up"],
+                down_prefetch_buffer=pools.prefetch["down"])
+            torch.cuda.current_stream().wait_event(ev)
+            slots = dict(g=pools.slot("gate"), u=pools.slot("up"), d=pools.slot("down"))
+        else:
+            slots = dict(g=None, u=None, d=None)
+        split = epn if slots["g"] is not None else None
+        cu_use = cu if split is not None else cu[:epn]
+        act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use,
+                                           wg_slot=slots["g"], wu_slot=slots["u"], split=split,
+                                           row_scale=w_nvs, save_gate_up=layer.training)
+        shard = buf.hidden_nvsh_buffer_view
+        gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split, out=shard)
+        y, _, _ = buf.combine(plan, shard, None, zero_copy=True)
+        ctx.layer, ctx.plan, ctx.split = layer, plan, split
+        ctx.save_for_backward(x, hidden, w_nvs, cu_use, act, gate, up, topk, w)
+        layer.last_plan = plan
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        layer, plan, split = ctx.layer, ctx.plan, ctx.split
+        buf: Buffer = layer.buf
+        pools = layer.pools
+        x, hidden, w_nvs, cu, act, gate, up, topk, w = ctx.saved_tensors
+        have_slots = split is not None
+        slot = (lambda n: pools.slot(n)) if have_slots else (lambda n: None)
+        gslot = (lambda n: pools.grad_slot(n)) if have_slots else (lambda n: None)
+        dy = dy.contiguous()
+        # combine backward = dispatch with the saved plan; the view is consumed before the shard
+        # is overwritten further down (same stream)
+        d_out, _, _, _ = buf.dispatch(dy, plan=plan, zero_copy=True)
+        d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split)
+        acc = layer.accumulate_grads
+        gemm.wgrad(d_out, act, cu, layer.g_down, grad_slot=gslot("down"), split=split, accumulate=acc)
+        d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
+        gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
+        gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
+        shard = buf.hidden_nvsh_buffer_view
+        gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
+                          wu_slot=slot("up"), split=split, out=shard)
+        # dispatch backward = combine; the weight-gather path returns d(route weights) [S, K]
+        dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
+        if have_slots and pools.reduce:
+            buf.reduce_grad(plan, local_gate_grad=layer.g_gate, local_up_grad=layer.g_up,
+                            local_down_grad=layer.g_down, gate_reduce_buffer=pools.reduce["gate"],
+                            up_reduce_buffer=pools.reduce["up"], down_reduce_buffer=pools.reduce["down"])
+        # router backward
+        d_logits = ew.router_topk_bwd(w, dw_sk, topk, buf.E)                 # [S, E] bf16
+        gemm.wgrad(x, d_logits, None, layer.g_router, accumulate=acc)
+        dx_r = gemm.dense(d_logits, layer.w_router, b_is_kn=False, out_dtype=torch.bfloat16)
+        dx = dx + dx_r
+        return dx, None
+
+
+class MoELayer:
+    """One MoE layer of ``E`` SwiGLU experts sharded over the ``R`` ranks of ``buf``."""
+
+    def __init__(self, buf: Buffer, Hp: int, pools: Optional[ExpertPools] = None, *, seed: int = 0,
+                 router_bias: Optional[torch.Tensor] = None, init_std: float = 0.02,
+                 train: bool = True):
+        assert not buf.virtual, "MoELayer runs one rank per process"
+        assert buf.token_padding % 64 == 0, "the grouped GEMM needs token_padding % 64 == 0"
+        assert buf.H % 128 == 0 and Hp % 64 == 0
+        self.buf, self.pools, self.Hp = buf, pools, Hp
+        self.training, self.accumulate_grads = train, False
+        dev = torch.device("cuda", buf.device)
+        H, E, epn = buf.H, buf.E, buf.epn
+        g = torch.Generator(device=dev).manual_seed(seed * 7919 + 13)
+        ge = torch.Generator(device=dev).manual_seed(seed * 7919 + 101 + buf.rank)
+        rnd = lambda gen, *s: (torch.randn(*s, device=dev, generator=gen) * init_std).bfloat16()
+        self.w_router = rnd(g, H, E)                       # replicated (same seed on every rank)
+        self.w_gate = rnd(ge, epn, H, Hp)
+        self.w_up = rnd(ge, epn, H, Hp)
+        self.w_down = rnd(ge, epn, H, Hp)
+        self.router_bias = router_bias
+        if train:
+            z = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)
+            self.g_router = z(1, H, E)
+            self.g_gate, self.g_up, self.g_down = z(epn, H, Hp), z(epn, H, Hp), z(epn, H, Hp)
+        self.last_plan = None
+
+    def parameters(self):
+        return dict(router=self.w_router, gate=self.w_gate, up=self.w_up, down=self.w_down)
+
+    def grads(self):
+        return dict(router=self.g_router[0], gate=self.g_gate, up=self.g_up, down=self.g_down)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        assert x.dtype == torch.bfloat16 and tuple(x.shape) == (self.buf.S, self.buf.H)
+        return _MoEFn.apply(x.contiguous(), self)
+
+    def sgd_step(self, lr: float) -> None:
+        """``w -= lr * grad`` on every parameter (the router grad is averaged over the group by
+        the caller if it wants data-parallel semantics; experts are rank-private)."""
+        ew.sgd_update_(self.w_router, self.g_router[0], lr)
+        ew.sgd_update_(self.w_gate, self.g_gate, lr)
+        ew.sgd_update_(self.w_up, self.g_up, lr)
+        ew.sgd_update_(self.w_down, self.g_down, lr)
+
+    def state_dict(self):
+        """Home-layout weights only; prefetch slots are transient and never saved."""
+        return {k: v.detach().cpu() for k, v in self.parameters().items()}
+
+    def load_state_dict(self, sd):
+        for k, v in self.parameters().items():
+            v.copy_(sd[k].to(v.device))

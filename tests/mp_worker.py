@@ -1,0 +1,196 @@
+"""Worker for the multi-GPU tests: run under ``python -m torch.distributed.run`` with one process
+per GPU.  Checks the real peer-memory paths (VMM handle exchange, NVLink stores / loads, flag
+barriers) against the CPU simulator, then the MoE layer against a dense fp32 reference."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from moonep_b200 import reference as ref  # noqa: E402
+from moonep_b200.api import Buffer  # noqa: E402
+from moonep_b200.utils.routing import routing_for_maxvio, tokens_per_expert  # noqa: E402
+
+
+def all_ok(ok: bool, what: str, detail=""):
+    """Collective assert: every rank learns about a failure, so nobody hangs in a later op."""
+    t = torch.tensor([int(ok)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if int(t) != 1:
+        raise AssertionError(f"{what} failed on rank {dist.get_rank()}: {detail}" if not ok
+                             else f"{what} failed on another rank")
+
+
+def comm_checks(R, rank):
+    S, H, K, tp = 256, 512, 4, 32
+    E = 8 * R
+    topk, w, mv, _ = routing_for_maxvio(S, K, E, R, 2.0, seed=11)
+    tpe = torch.stack([tokens_per_expert(topk[r], E) for r in range(R)])
+    x = torch.randn(R, S, H, generator=torch.Generator().manual_seed(5)).bfloat16()
+    sim = ref.SimGroup(S, H, K, E, R, tp)
+    h_ref, w_ref, cu_ref, plans_ref = sim.dispatch(x, w, topk)
+    buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=tp, timeout_s=10.0)
+    xd, wd, td, pd = x[rank].cuda(), w[rank].cuda(), topk[rank].cuda(), tpe[rank].cuda()
+    hidden, w_nvs, cu, plan = buf.dispatch(xd, wd, td, pd)
+    buf.check()
+    rows = int(cu_ref[rank, -1])
+    pr = plans_ref[rank]
+    all_ok(torch.equal(plan.dst.cpu(), pr.dst), "plan.dst")
+    all_ok(torch.equal(cu.cpu(), cu_ref[rank]), "cu_seqlens")
+    all_ok(torch.equal(plan.experts_to_copy.cpu(), pr.experts_to_copy), "experts_to_copy")
+    all_ok(torch.equal(plan.zero_fill_ranges.cpu(), pr.zero_fill_ranges), "zero_fill")
+    all_ok(torch.equal(plan.remote_stats.cpu(), pr.remote_stats), "remote_stats")
+    all_ok(torch.equal(hidden.cpu()[:rows], h_ref[rank, :rows]), "dispatched rows")
+    all_ok(torch.equal(w_nvs.cpu()[:rows], w_ref[rank, :rows]), "dispatched weights")
+    all_ok(torch.equal(plan.link.cpu()[:rows], pr.link[:rows]), "chain links")
+    y = (hidden.float() * w_nvs[:, None]).bfloat16()
+    out, w_back, _ = buf.combine(plan, y, w_nvs)
+    buf.check()
+    y_ref = (h_ref.float() * w_ref[:, :, None]).bfloat16()
+    out_ref, wb_ref = sim.combine(plans_ref, y_ref, w_ref)
+    all_ok(torch.equal(out.cpu().view(torch.int16), out_ref[rank].view(torch.int16)), "combine")
+    all_ok(torch.equal(w_back.cpu(), w[rank]), "weight gather")
+    # async + plan reuse + zero copy
+    h2, _, cu2, plan2, ev = buf.dispatch(xd, None, plan=plan, async_finish=True, zero_copy=True)
+    ev.wait()
+    all_ok(cu2 is None and plan2 is plan, "plan reuse contract")
+    out2, _, ev2 = buf.combine(plan, h2, None, async_finish=True, zero_copy=True)
+    ev2.wait()
+    torch.cuda.synchronize()
+    ident = (x[rank].float() * K).bfloat16()
+    err = float((out2.cpu().float() - ident.float()).abs().max())
+    all_ok(err <= 2 * 2 ** -7 * float(ident.float().abs().max()), "identity round trip", err)
+    # ---- prefetch + reduce_grad with the real plan -------------------------------------------
+    from moonep_b200.models.moe_layer import ExpertPools
+    epn, Hh, Hp = E // R, 128, 256
+    pools = ExpertPools(R, epn, Hh, Hp, buf.group, rank)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    loc = {n: torch.randn(epn, Hh, Hp, device="cuda", generator=g).bfloat16() for n in pools.names}
+    for n in pools.names:
+        pools.prefetch[n][rank].fill_(-3.0)
+    torch.cuda.synchronize(); dist.barrier()
+    buf.prefetch_weight(plan, local_gate_weight=loc["gate"], local_up_weight=loc["up"],
+                        local_down_weight=loc["down"], gate_prefetch_buffer=pools.prefetch["gate"],
+                        up_prefetch_buffer=pools.prefetch["up"], down_prefetch_buffer=pools.prefetch["down"])
+    buf.check()
+    etc = pr.experts_to_copy
+    allw = {}
+    for n in pools.names:
+        lst = [torch.empty_like(loc[n]) for _ in range(R)]
+        dist.all_gather(lst, loc[n])
+        allw[n] = torch.cat(lst)                                  # [E, Hh, Hp]
+    ok = True
+    for n in pools.names:
+        for b in range(epn):
+            e = int(etc[rank, b])
+            got = pools.prefetch[n][rank, b]
+            ok &= torch.equal(got, allw[n][e]) if e >= 0 else bool((got == -3.0).all())
+    all_ok(ok, "prefetch_weight")
+    lg = {n: torch.randn(epn, Hh, Hp, device="cuda", generator=g) for n in pools.names}
+    lg0 = {n: v.clone() for n, v in lg.items()}
+    for n in pools.names:
+        pools.reduce[n][rank].copy_(torch.randn(epn, Hh, Hp, device="cuda", generator=g))
+    torch.cuda.synchronize(); dist.barrier()
+    snap = {n: pools.reduce[n].clone() for n in pools.names}     # all ranks' slots, read over NVLink
+    torch.cuda.synchronize(); dist.barrier()
+    buf.reduce_grad(plan, local_gate_grad=lg["gate"], local_up_grad=lg["up"], local_down_grad=lg["down"],
+                    gate_reduce_buffer=pools.reduce["gate"], up_reduce_buffer=pools.reduce["up"],
+                    down_reduce_buffer=pools.reduce["down"])
+    buf.check()
+    ok = True
+    for n in pools.names:
+        want = lg0[n].clone()
+        for d in range(R):
+            for b in range(epn):
+                e = int(etc[d, b])
+                if e >= 0 and e // epn == rank:
+                    want[e % epn] += snap[n][d, b]
+        ok &= torch.equal(lg[n], want)
+        for b in range(epn):
+            if int(etc[rank, b]) >= 0:
+                ok &= bool((pools.reduce[n][rank, b] == 0).all())
+            else:
+                ok &= torch.equal(pools.reduce[n][rank, b], snap[n][rank, b])
+    all_ok(ok, "reduce_grad (bitwise)")
+    st = buf.stats()
+    all_ok(st["dispatch"] == 2 and st["combine"] == 2, "stats")
+    buf.destroy()
+
+
+def layer_check(R, rank):
+    from moonep_b200.models.moe_layer import ExpertPools, MoELayer
+    from moonep_b200.ops import gemm
+    from tests.test_moe_layer import reference_layer
+    S, H, Hp, K = 256, 256, 128, 4
+    E = 4 * R
+    buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=64, timeout_s=10.0)
+    pools = ExpertPools(R, E // R, H, Hp, buf.group, rank)
+    # a strong bias towards the experts of rank 0 forces redundant experts and prefetch slots
+    bias = torch.zeros(E, device="cuda")
+    bias[: E // R] = 1.5
+    layer = MoELayer(buf, Hp, pools, seed=5, init_std=0.06, router_bias=bias)
+    g = torch.Generator(device="cuda").manual_seed(50 + rank)
+    x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    dy = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    xo = x.clone().requires_grad_(True)
+    y = layer(xo)
+    y.backward(dy)
+    buf.check()
+    gemm.check_status()
+    used = int((layer.last_plan.experts_to_copy >= 0).sum())
+    gather = lambda t: torch.cat([u for u in _all_gather(t, R)])
+    wg, wu, wd = gather(layer.w_gate), gather(layer.w_up), gather(layer.w_down)
+    xs, dys = _all_gather(x, R), _all_gather(dy, R)
+    wr = layer.w_router.float().clone().requires_grad_(True)
+    wgf, wuf, wdf = [t.float().clone().requires_grad_(True) for t in (wg, wu, wd)]
+    mine = None
+    for r in range(R):                     # global reference: every rank's tokens through all experts
+        xr = xs[r].float().requires_grad_(True)
+        yr, _ = reference_layer(xr, wr, wgf, wuf, wdf, K, bias)
+        yr.backward(dys[r].float())
+        if r == rank:
+            mine = (yr.detach(), xr.grad)
+    epn = E // R
+
+    def rel(a, b):
+        return float((a.float() - b).abs().max()) / (float(b.abs().max()) + 1e-9)
+
+    errs = dict(y=rel(y, mine[0]), dx=rel(xo.grad, mine[1]),
+                gate=rel(layer.g_gate, wgf.grad[rank * epn:(rank + 1) * epn]),
+                up=rel(layer.g_up, wuf.grad[rank * epn:(rank + 1) * epn]),
+                down=rel(layer.g_down, wdf.grad[rank * epn:(rank + 1) * epn]))
+    all_ok(max(errs.values()) < 6e-2, "MoE layer vs dense reference", str(errs))
+    tot = torch.tensor([used], device="cuda")
+    dist.all_reduce(tot)
+    all_ok(int(tot) > 0, "skewed routing must create redundant experts", f"slots used {int(tot)}")
+    if rank == 0:
+        print(f"layer R={R}: errs {errs}, prefetch slots in use {int(tot) // R}", flush=True)
+    buf.destroy()
+
+
+def _all_gather(t, R):
+    lst = [torch.empty_like(t) for _ in range(R)]
+    dist.all_gather(lst, t.contiguous())
+    return lst
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    R, rank = dist.get_world_size(), dist.get_rank()
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("all", "comm"):
+        comm_checks(R, rank)
+    if what in ("all", "layer"):
+        layer_check(R, rank)
+    dist.barrier()
+    if rank == 0:
+        print(f"MULTIGPU_OK R={R} {what}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
