@@ -18,6 +18,7 @@ explicit ``release()``.
 """
 from __future__ import annotations
 
+import array
 import ctypes
 import os
 import shutil
@@ -124,7 +125,11 @@ def exchange_fds(fd: int, group, tag: str = "h") -> list[int]:
         dist.barrier(group=group)           # every socket is bound
         for r in range(R):
             if r != rank:
-                socket.send_fds(sock, [rank.to_bytes(4, "little")], [fd], address=path(r))
+                # sendmsg directly: socket.send_fds() drops its address argument on some
+                # Python versions, which a datagram socket cannot live without
+                sock.sendmsg([rank.to_bytes(4, "little")],
+                             [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", [fd]))],
+                             0, path(r))
         out[rank] = fd
         for _ in range(R - 1):
             try:

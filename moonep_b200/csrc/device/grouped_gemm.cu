@@ -117,7 +117,7 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     t.rows = min(BM, s_end[t.g] - t.row0);
     t.m0 = 0;
     t.n0 = ni * (EPI == EPI_SWIGLU ? BN / 2 : BN);
-    t.num_kb = p.nseg * (p.K / BK);
+    t.num_kb = p.nseg * ((p.K + BK - 1) / BK);
   }
   t.alloc = t.g >= p.split ? 1 : 0;
   t.g_local = t.alloc ? t.g - p.split : t.g;
@@ -195,7 +195,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       for (long long id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
         Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
         if (!t.valid) continue;
-        const int kb_per_seg = WGRAD ? t.num_kb : p.K / BK;
+        const int kb_per_seg = WGRAD ? t.num_kb : (p.K + BK - 1) / BK;
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % GEMM_STAGES;
           if (it >= GEMM_STAGES &&
@@ -505,7 +505,9 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
     if (d->epi != EPI_F32) return fail(-3, "wgrad writes fp32");
     return launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
   }
-  if (d->K % BK != 0) return fail(-4, "gemm: K=%d must be a multiple of %d", d->K, BK);
+  // A reduction tail is legal: the TMA loads zero-fill A beyond K, which also cancels whatever
+  // a MN-major B tile picks up from the next expert's rows.
+  if (d->K % 8 != 0) return fail(-4, "gemm: K=%d must be a multiple of 8", d->K);
   if (d->nseg < 1 || d->nseg > 2) return fail(-5, "gemm: nseg=%d", d->nseg);
   for (int s = 0; s < d->nseg; ++s)
     if ((rc = make_map(&kp.a[s], d->a[s], d->a_rows, d->K, d->lda[s], BK, BM))) return rc;

@@ -16,7 +16,7 @@ op                        math                        operands
 
 Groups are the VM groups of ``cu_seqlens``; ``*_slot`` tensors are this rank's prefetch / reduce
 slots and serve groups ``>= split`` (they may be ``None`` when the plan never uses them).
-Requirements: bf16 operands, 16-byte aligned, reduction length a multiple of 64, group sizes a
+Requirements: bf16 operands, 16-byte aligned, reduction length a multiple of 8, group sizes a
 multiple of 64 for ``wgrad``.  Every call raises if the native library is missing; there is no
 eager fallback.
 """
