@@ -143,9 +143,9 @@ class Buffer:
             self.meta_buf = symm.create_local_group_tensor((meta_ints,), torch.int32, R, self.device)
             self.meta_mc = None
         else:
-            self.hidden_buf = symm.create_nvl_dist_tensor((self.NvS, H), torch.bfloat16, self.group, self.device)
+            self.hidden_buf = symm.create_nvl_dist_tensor((self.NvS, H), torch.bfloat16, group=self.group, device=self.device)
             self.meta_buf, self.meta_mc = symm.create_nvl_dist_multicast_tensor(
-                (meta_ints,), torch.int32, self.group, self.device)
+                (meta_ints,), torch.int32, group=self.group, device=self.device)
         self.hidden_stride = self.hidden_buf.shape[0] // R
         self.meta_stride = self.meta_buf.shape[0] // R
         offs = (ctypes.c_int64 * 5)()

@@ -67,21 +67,36 @@ def _check(rc: int, what: str) -> None:
         raise SymmetricMemoryError(f"{what}: {nat.last_error()} (code {rc})")
 
 
-def get_vmm_granularity(device: int, fabric: bool = False) -> int:
+def get_vmm_granularity(device: Optional[int] = None, fabric: bool = False) -> int:
+    device = torch.cuda.current_device() if device is None else device
     g = nat.call("mep_vmm_granularity", device, int(fabric))
     if g <= 0:
         raise SymmetricMemoryError(f"granularity query failed: {nat.last_error()}")
     return int(g)
 
 
-def pad_to_granularity(nbytes: int, granularity: int) -> int:
+def pad_to_granularity(nbytes: int, granularity: Optional[int] = None) -> int:
+    """Round ``nbytes`` up to the VMM granularity (moonep/buffer.py:89)."""
+    granularity = get_vmm_granularity() if granularity is None else granularity
     return (nbytes + granularity - 1) // granularity * granularity
 
 
-def pad_dim0_for_alignment(dim0: int, row_bytes: int, granularity: int) -> int:
-    """Smallest ``d >= dim0`` such that ``d * row_bytes`` is a multiple of ``granularity``."""
+def pad_dim0_for_alignment(chunk_shape, dtype, granularity: Optional[int] = None) -> int:
+    """Smallest ``d >= dim0`` such that a chunk of ``d`` rows is a whole number of VMM granules.
+
+    Called like the reference, ``pad_dim0_for_alignment([epn, H, Hp], torch.bfloat16)``
+    (moonep/buffer.py:95), or with plain numbers, ``pad_dim0_for_alignment(dim0, row_bytes, gran)``.
+    """
     import math
 
+    if isinstance(chunk_shape, (list, tuple, torch.Size)):
+        dim0 = int(chunk_shape[0])
+        row_bytes = torch.empty((), dtype=dtype).element_size()
+        for d in chunk_shape[1:]:
+            row_bytes *= int(d)
+    else:
+        dim0, row_bytes = int(chunk_shape), int(dtype)
+    granularity = get_vmm_granularity() if granularity is None else granularity
     step = granularity // math.gcd(granularity, row_bytes)
     return (dim0 + step - 1) // step * step
 
@@ -318,11 +333,25 @@ def _exchange_and_map(local_handle: int, chunk_bytes: int, group, device: int, f
     return handles, va
 
 
-def create_nvl_dist_tensor(shape, dtype, group=None, device: Optional[int] = None) -> torch.Tensor:
-    """Symmetric tensor ``[R * rows, *shape[1:]]``: slice ``r`` is rank ``r``'s memory."""
+def create_nvl_dist_tensor(shape, dtype, local_rank=None, world_size=None, group=None,
+                           device: Optional[int] = None) -> torch.Tensor:
+    """Symmetric tensor ``[R * rows, *shape[1:]]``: slice ``r`` is rank ``r``'s memory.
+
+    Accepts the reference's call ``create_nvl_dist_tensor(chunk_shape, dtype, rank, R, group)``
+    (moonep/buffer.py:217); ``rank`` / ``R`` are then checked against the group.  Unlike the
+    reference, a ``shape[0]`` that is not granule-aligned is padded (``rows >= shape[0]``).
+    """
+    if local_rank is not None and not isinstance(local_rank, int):
+        group, local_rank = local_rank, None          # (shape, dtype, group) call style
+    if not dist.is_initialized():
+        assert world_size in (None, 1), "a process group is required for more than one rank"
+        device = torch.cuda.current_device() if device is None else device
+        return create_local_group_tensor(shape, dtype, 1, device)
     group = group if group is not None else dist.group.WORLD
     device = torch.cuda.current_device() if device is None else device
     R = dist.get_world_size(group)
+    assert world_size in (None, R), f"world_size={world_size} but the group has {R} ranks"
+    assert local_rank in (None, dist.get_rank(group)), "local_rank does not match the group"
     if R == 1:
         return create_local_group_tensor(shape, dtype, 1, device)
     if not nat.call("mep_vmm_supported", device):
@@ -337,7 +366,8 @@ def create_nvl_dist_tensor(shape, dtype, group=None, device: Optional[int] = Non
     return t
 
 
-def create_nvl_dist_multicast_tensor(shape, dtype, group=None, device: Optional[int] = None):
+def create_nvl_dist_multicast_tensor(shape, dtype, local_rank=None, world_size=None, group=None,
+                                     device: Optional[int] = None):
     """``(tensor, multicast_alias | None)``.
 
     The alias addresses the NVSwitch multicast object bound to every rank's chunk: a
@@ -346,9 +376,11 @@ def create_nvl_dist_multicast_tensor(shape, dtype, group=None, device: Optional[
     dies while its memory is bound to a multicast object can fault its peers, so the overlay is
     opt-in).
     """
+    if local_rank is not None and not isinstance(local_rank, int):
+        group, local_rank = local_rank, None
     group = group if group is not None else dist.group.WORLD
     device = torch.cuda.current_device() if device is None else device
-    t = create_nvl_dist_tensor(shape, dtype, group, device)
+    t = create_nvl_dist_tensor(shape, dtype, local_rank, world_size, group, device)
     R = dist.get_world_size(group)
     want = os.environ.get("MOONEP_B200_NVLS") == "1"
     if R == 1 or not want or not nat.call("mep_multicast_supported", device):

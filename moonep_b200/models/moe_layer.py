@@ -43,10 +43,10 @@ class ExpertPools:
         if R == 1:
             return
         for n in self.names:
-            t = symm.create_nvl_dist_tensor((epn, H, Hp), torch.bfloat16, group)
+            t = symm.create_nvl_dist_tensor((epn, H, Hp), torch.bfloat16, group=group)
             self.prefetch[n] = t.view(R, t.shape[0] // R, H, Hp)[:, :epn]
             if train:
-                g = symm.create_nvl_dist_tensor((epn, H, Hp), torch.float32, group)
+                g = symm.create_nvl_dist_tensor((epn, H, Hp), torch.float32, group=group)
                 gv = g.view(R, g.shape[0] // R, H, Hp)[:, :epn]
                 gv[rank].zero_()
                 self.reduce[n] = gv
