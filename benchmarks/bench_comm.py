@@ -107,6 +107,24 @@ def main():
                 fwd_dispatch()
                 buf.combine(st["plan"], st["h"], None, zero_copy=True)
         row["roundtrip_us"] = timed(roundtrip)
+        # per-kernel breakdown (the launchers the API calls, timed one by one)
+        from moonep_b200 import _native as nat
+        stream = lambda: torch.cuda.current_stream().cuda_stream
+        out_sh = torch.empty(S, H, dtype=torch.bfloat16, device=dev)
+        row["k_sync_us"] = timed(lambda: nat.call("mep_launch_sync", buf._ctx, stream()))
+        row["k_plan_us"] = timed(lambda: (nat.call(
+            "mep_launch_plan", buf._ctx, topk.data_ptr(), tpe.data_ptr(), plan.dst.data_ptr(),
+            plan.cu_seqlens.data_ptr(), plan.zero_fill_ranges.data_ptr(), plan.experts_to_copy.data_ptr(),
+            plan.remote_stats.data_ptr(), stream()), nat.call("mep_launch_sync", buf._ctx, stream())))
+        row["k_dispatch_us"] = timed(lambda: nat.call(
+            "mep_launch_dispatch", buf._ctx, x.data_ptr(), 0, plan.dst.data_ptr(),
+            plan.zero_fill_ranges.data_ptr(), 0, 1, 0, stream()))
+        row["k_expand_us"] = timed(lambda: nat.call(
+            "mep_launch_expand", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), stream()))
+        row["k_prologue_us"] = timed(lambda: nat.call(
+            "mep_launch_combine_prologue", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), stream()))
+        row["k_combine_us"] = timed(lambda: nat.call(
+            "mep_launch_combine", buf._ctx, plan.dst.data_ptr(), out_sh.data_ptr(), 0, stream()))
         etc = plan.experts_to_copy
         row["remote_experts_max_per_rank"] = int((etc >= 0).sum(1).max())
         row["remote_experts_total"] = int((etc >= 0).sum())

@@ -73,15 +73,37 @@ __global__ void __launch_bounds__(PROLOGUE_THREADS) ep_combine_prologue_kernel(c
     n = __shfl_sync(0xffffffffu, n, 0);
     __syncwarp();
     uint4* prim = shard + (size_t)r * nvec;
-    for (int v = lane; v < nvec; v += 32) {
-      float acc[8], t[8];
-      bf16x8_to_f32(prim[v], acc);
-      for (int i = 0; i < n; ++i) {
-        bf16x8_to_f32(shard[(size_t)chain[warp][i] * nvec + v], t);
+    // four independent 16-byte columns per lane and pass: (1 + n) * 4 loads in flight
+    for (int v0 = lane; v0 < nvec; v0 += 128) {
+      float acc[4][8];
+      uint4 raw[4];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] += t[q];
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + 32 * u;
+        raw[u] = v < nvec ? prim[v] : make_uint4(0, 0, 0, 0);
       }
-      prim[v] = f32_to_bf16x8(acc);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) bf16x8_to_f32(raw[u], acc[u]);
+      for (int i = 0; i < n; ++i) {
+        const uint4* drow = shard + (size_t)chain[warp][i] * nvec;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + 32 * u;
+          raw[u] = v < nvec ? drow[v] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float t[8];
+          bf16x8_to_f32(raw[u], t);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[u][q] += t[q];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + 32 * u;
+        if (v < nvec) prim[v] = f32_to_bf16x8(acc[u]);
+      }
     }
     __syncwarp();
   }
@@ -134,9 +156,10 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
   if (warp == 0) {
     // ---- loader: one remote bulk read per primary entry -----------------------------------
     int prod = 0;
+    int d_next = (n_tok > 0 && lane < p.K) ? dst[(size_t)c * p.K + lane] : -1;
     for (int j = 0; j < n_tok; ++j) {
-      const int t = c + j * G;
-      int d = lane < p.K ? dst[(size_t)t * p.K + lane] : -1;
+      const int d = d_next;   // the next token's destinations are fetched while this one is issued
+      d_next = (j + 1 < n_tok && lane < p.K) ? dst[(size_t)(c + (int64_t)(j + 1) * G) * p.K + lane] : -1;
       unsigned prim = __ballot_sync(0xffffffffu, d >= 0);
       while (prim) {
         int k = __ffs(prim) - 1;

@@ -79,22 +79,28 @@ def routing_for_maxvio(S, K, E, R, target, seed=0, dev="cpu", tol=0.05, iters=24
     """Search the Zipf exponent so that the global MaxVio is close to ``target``.
 
     Returns ``(topk[R,S,K] int32, weights[R,S,K] fp32, achieved_maxvio, alpha)``.
-    ``target <= 0`` returns the balanced round-robin routing with uniform weights.
+    ``target <= 0`` returns the balanced round-robin routing with uniform weights.  The N(0,1)
+    part of the logits is drawn once; only the popularity term changes during the search.
     """
     if target <= 0:
         tk = torch.stack([generate_topk_routing(S, K, E, R, 0.0, "cpu", seed, r)[0]
                           for r in range(R)])
         w = torch.full((R, S, K), 1.0 / K)
         return tk.to(dev), w.to(dev), maxvio(tokens_per_expert(tk, E)), 0.0
-    lo, hi = 0.0, 4.0
+    g_shared = torch.Generator(device="cpu").manual_seed(seed)
+    order = torch.randperm(E, generator=g_shared)
+    logpop = torch.empty(E)
+    logpop[order] = -torch.log(torch.arange(1, E + 1, dtype=torch.float32))
+    base = torch.stack([torch.randn(S, E, generator=torch.Generator().manual_seed(seed * 1000003 + r + 1))
+                        for r in range(R)])
+    lo, hi = 0.0, 6.0
     best = None
     for _ in range(iters):
         mid = 0.5 * (lo + hi)
-        pairs = [zipf_topk(S, K, E, mid, seed, r) for r in range(R)]
-        tk = torch.stack([p[0] for p in pairs])
-        mv = maxvio(tokens_per_expert(tk, E))
+        val, idx = torch.topk(base + mid * logpop, K, dim=2)
+        mv = maxvio(tokens_per_expert(idx, E))
         if best is None or abs(mv - target) < abs(best[2] - target):
-            best = (tk, torch.stack([p[1] for p in pairs]), mv, mid)
+            best = (idx.to(torch.int32), torch.softmax(val, dim=2), mv, mid)
         if abs(mv - target) <= tol * max(target, 1.0):
             break
         if mv < target:
@@ -102,4 +108,4 @@ def routing_for_maxvio(S, K, E, R, target, seed=0, dev="cpu", tol=0.05, iters=24
         else:
             hi = mid
     tk, w, mv, alpha = best
-    return tk.to(dev), w.to(dev), mv, alpha
+    return tk.contiguous().to(dev), w.contiguous().to(dev), mv, alpha
