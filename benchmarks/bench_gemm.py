@@ -41,8 +41,10 @@ def main():
     ap.add_argument("--Hp", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default="")
+    ap.add_argument("--debug-mode", type=int, default=0, help="kernel timing experiment (results are wrong)")
     args = ap.parse_args()
     G, rpg, H, Hp = args.groups, args.rows_per_group, args.H, args.Hp
+    gemm.DEBUG_MODE = args.debug_mode
     rows = G * rpg
     dev = "cuda"
     peaks = {}
@@ -79,14 +81,18 @@ def main():
         ms = timeit(fn, args.iters, flush=flush)
         out[name] = {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
                      "frac_of_measured_peak": round(flops / ms / 1e9 / peak, 3)}
-    nbytes = rows * Hp * 2 * 5 + rows * 4
-    ms = timeit(lambda: ew.swiglu_bwd(act, gate, up, rs), args.iters, flush=flush)
-    out["swiglu_bwd"] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
-                         "frac_of_measured_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
     n = G * H * Hp
-    ms = timeit(lambda: ew.sgd_update_(wg, grad, 1e-6), args.iters, flush=flush)
-    out["sgd_update"] = {"ms": round(ms, 4), "gbs": round(n * 8 / ms / 1e6, 1),
-                         "frac_of_measured_hbm": round(n * 8 / ms / 1e6 / hbm, 3)}
+    if not args.only:
+        nbytes = rows * Hp * 2 * 5 + rows * 4
+        ms = timeit(lambda: ew.swiglu_bwd(act, gate, up, rs), args.iters, flush=flush)
+        out["swiglu_bwd"] = {"ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+                             "frac_of_measured_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+        ms = timeit(lambda: ew.sgd_update_(wg, grad, 1e-6), args.iters, flush=flush)
+        out["sgd_update"] = {"ms": round(ms, 4), "gbs": round(n * 8 / ms / 1e6, 1),
+                             "frac_of_measured_hbm": round(n * 8 / ms / 1e6 / hbm, 3)}
+    if not args.only:
+        ms = timeit(lambda: grad.zero_(), args.iters, flush=flush)
+        out["hbm_write_only(torch zero_)"] = {"ms": round(ms, 4), "gbs": round(n * 4 / ms / 1e6, 1)}
     torch.cuda.synchronize()
     gemm.check_status()
     print(json.dumps(out))

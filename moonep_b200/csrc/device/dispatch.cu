@@ -249,7 +249,8 @@ int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_s
   p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
   p.rank_base = c.virt ? 0 : c.rank;
   p.hidden = (__nv_bfloat16*)c.hidden; p.link = link; p.cu_seqlens = cu_seqlens;
-  dim3 grid(c.num_sms_local, c.Rv());
+  // latency-bound row walks: several CTAs per SM keep enough loads in flight
+  dim3 grid(c.num_sms_local * 6, c.Rv());
   ep_expand_kernel<<<grid, EXPAND_THREADS, 0, stream>>>(p);
   MEP_CUDA_OK(cudaGetLastError());
   return 0;

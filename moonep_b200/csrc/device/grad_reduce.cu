@@ -124,15 +124,21 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
         int t, le; int64_t off; uint32_t bytes;
         decode(j, t, le, off, bytes);
         const int ns = cnt[le];
-        for (int q = 0; q < ns; ++q, ++prod) {
+        // entry -1 is the local grad chunk itself: it seeds the accumulators, so the home
+        // rank's own read is pipelined with the remote ones instead of stalling each item
+        for (int q = -1; q < ns; ++q, ++prod) {
           const int s = prod % ST;
           if (prod >= ST) mbar_wait(sc, &empty[s], ((uint32_t)(prod / ST) & 1u) ^ 1u, 20);
-          int slot = srcs[start[le] + q];
-          int d = slot / epn, b = slot - d * epn;
+          const float* src;
+          if (q < 0) {
+            src = p.local[t] + ((size_t)vr * epn + le) * p.expert_elems[t] + off;
+          } else {
+            int slot = srcs[start[le] + q];
+            int d = slot / epn, b = slot - d * epn;
+            src = p.pool[t] + (size_t)d * p.rank_stride[t] + (size_t)b * p.expert_elems[t] + off;
+          }
           mbar_expect_tx(&full[s], bytes);
-          bulk_g2s(ring + (size_t)s * GR_CHUNK,
-                   p.pool[t] + (size_t)d * p.rank_stride[t] + (size_t)b * p.expert_elems[t] + off,
-                   bytes, &full[s]);
+          bulk_g2s(ring + (size_t)s * GR_CHUNK, src, bytes, &full[s]);
         }
       }
     }
@@ -145,13 +151,8 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
       const int nvec = (int)(bytes / 16);
       float4* g = reinterpret_cast<float4*>(p.local[t] + ((size_t)vr * epn + le) * p.expert_elems[t] + off);
       float4 acc[GR_VEC_PER_THREAD];
-#pragma unroll
-      for (int i = 0; i < GR_VEC_PER_THREAD; ++i) {
-        int v = ta + i * GR_ACC_THREADS;
-        acc[i] = v < nvec ? g[v] : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
       const int ns = cnt[le];
-      for (int q = 0; q < ns; ++q, ++cons) {
+      for (int q = -1; q < ns; ++q, ++cons) {
         const int s = cons % ST;
         mbar_wait(sc, &full[s], (uint32_t)(cons / ST) & 1u, 30);
         const float4* src = reinterpret_cast<const float4*>(ring + (size_t)s * GR_CHUNK);
@@ -160,7 +161,11 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
           int v = ta + i * GR_ACC_THREADS;
           if (v < nvec) {
             float4 x = src[v];
-            acc[i].x += x.x; acc[i].y += x.y; acc[i].z += x.z; acc[i].w += x.w;
+            if (q < 0) {
+              acc[i] = x;
+            } else {
+              acc[i].x += x.x; acc[i].y += x.y; acc[i].z += x.z; acc[i].w += x.w;
+            }
           }
         }
         __syncwarp();

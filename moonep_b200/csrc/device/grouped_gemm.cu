@@ -38,7 +38,7 @@ constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
-constexpr int MAX_GROUPS = 2048;
+constexpr int MAX_GROUPS = 1024;
 constexpr int GEMM_SMEM = GEMM_STAGES * STAGE_BYTES + 1024;
 
 enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
@@ -46,8 +46,10 @@ enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
 struct GemmKParams {
   CUtensorMap a[2];
   CUtensorMap b[2][2];
+  CUtensorMap c[2];        // weight-grad output (fp32), per allocation
   const int32_t* cu_seqlens;
   int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
+  int debug;   // timing experiments only: 1 = skip epilogue stores, 2 = skip TMEM loads
   void* out[3];
   const float* row_scale;
   long long ldc;
@@ -136,6 +138,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ int s_abort;
   __shared__ int s_end[MAX_GROUPS];
   __shared__ int s_prefix[MAX_GROUPS + 1];
+  __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];   // per-warp staging pad
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -351,6 +354,77 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           col_base = t.n0;
         }
         void* outp = WGRAD ? p.out[t.alloc] : p.out[0];
+        if constexpr (EPI == EPI_F32 && WGRAD) {
+          // fp32 weight-grad tiles are 128 KB each and the main loop is short (one group's
+          // tokens), so the epilogue must move ~30 GB/s per SM.  Four warps of plain stores
+          // cannot (measured: ~14 B/clk/SM), so each warp stages 32x32 blocks in shared memory
+          // (128-byte swizzle, conflict-free 16-byte stores) and hands them to the TMA engine:
+          // a tiled store, or a tiled reduce-add when accumulating into existing grads.
+          uint8_t* pad = reinterpret_cast<uint8_t*>(s_epi) + q * 4096;
+          const int y0 = t.g_local * p.Mw + t.m0 + q * 32;
+          const CUtensorMap* cmap = &p.c[t.alloc];
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            if (have_acc && p.debug != 2) {
+              tmem_ld_32x32(tacc + c * 32, r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            if (lane == 0) bulk_wait_read<0>();     // the previous block has left the pad
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(pad + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            const int x0 = col_base + c * 32;
+            if (lane == 0 && x0 < p.N && p.debug != 1) {
+              if (p.accumulate) tma_reduce_add_2d(cmap, x0, y0, pad);
+              else tma_store_2d(cmap, x0, y0, pad);
+              bulk_commit();
+            }
+          }
+        } else if constexpr (EPI == EPI_F32) {
+          // token-major fp32 output (router logits): rows of a tile may belong to the next
+          // group, so stores stay row-masked; each warp transposes through a padded pad so
+          // that every store instruction writes one full 128-byte line.
+          float* pad = s_epi + q * (32 * 33);
+          const long long row_stride = p.ldc;
+          const long long off_warp = WGRAD ? ((long long)t.g_local * p.Mw + t.m0 + q * 32) * p.ldc
+                                           : ((long long)t.row0 + q * 32) * p.ldc;
+          const int rows_ok = WGRAD ? min(32, p.Mw - (t.m0 + q * 32)) : min(32, t.rows - q * 32);
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            if (have_acc && p.debug != 2) {
+              tmem_ld_32x32(tacc + c * 32, r);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = 0u;
+            }
+            const int col = col_base + c * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pad[lane * 33 + i] = __uint_as_float(r[i]);
+            __syncwarp();
+            if (col < p.N && p.debug != 1) {
+              float* o = (float*)outp + off_warp + col;
+#pragma unroll 8
+              for (int rr = 0; rr < 32; ++rr) {
+                if (rr < rows_ok) {
+                  float v = pad[rr * 33 + lane];
+                  if (p.accumulate) v += o[rr * row_stride];
+                  o[rr * row_stride] = v;
+                }
+              }
+            }
+            __syncwarp();
+          }
+        } else
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -364,22 +438,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           const int col = col_base + c * 32;
           if (!row_ok || col >= p.N) continue;
           if constexpr (EPI == EPI_F32) {
-            float* o = (float*)outp + off_row + col;
-            if (col + 32 <= p.N) {
-#pragma unroll
-              for (int v = 0; v < 8; ++v) {
-                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-                if (p.accumulate) {
-                  float4 y = reinterpret_cast<float4*>(o)[v];
-                  x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-                }
-                reinterpret_cast<float4*>(o)[v] = x;
-              }
-            } else {
-              for (int i = 0; i < 32 && col + i < p.N; ++i)
-                o[i] = __uint_as_float(r[i]) + (p.accumulate ? o[i] : 0.f);
-            }
+            // unreachable: the fp32 epilogue is the transposed loop below
           } else {
             __nv_bfloat16* o = (__nv_bfloat16*)outp + off_row + col;
             uint32_t pk[16];
@@ -412,6 +471,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 200000ull) { }
   }
+  if (warp >= 2 && lane == 0) bulk_wait<0>();   // epilogue TMA stores have completed
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -422,6 +482,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 struct GemmDesc {
   int32_t mode, epi, b_mn, nseg;
   int32_t ngroups, split, total_rows, N, K, rows_per_expert, Mw, accumulate, zero_empty_below, grid;
+  int32_t debug, pad_;
   int64_t a_rows;
   int64_t lda[2];
   const void* a[2];
@@ -440,6 +501,23 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                              CUtensorMapFloatOOBfill);
+
+// 2-D fp32 tensor [rows][cols], box 32 x 32 (128-byte rows), 128B swizzle: weight-grad output.
+static int make_map_f32(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeFn enc = (EncodeFn)driver_tensor_map_encode();
+  if (!enc) return fail(-10, "CUDA driver entry cuTensorMapEncodeTiled not available");
+  if (((uintptr_t)base & 15) != 0 || (ld * 4) % 16 != 0)
+    return fail(-11, "weight-grad output must be 16-byte aligned with a 16-byte multiple row stride");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(-12, "cuTensorMapEncodeTiled (fp32) failed with code %d", (int)r);
+  return 0;
+}
 
 // 2-D bf16 tensor [rows][cols] (row stride ld elements), box [box_rows][box_cols], 128B swizzle.
 static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld,
@@ -488,6 +566,7 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
   kp.total_rows = d->total_rows; kp.N = d->N; kp.K = d->K; kp.nseg = d->nseg;
   kp.rows_per_expert = d->rows_per_expert; kp.Mw = d->Mw; kp.accumulate = d->accumulate;
   kp.zero_empty_below = d->zero_empty_below;
+  kp.debug = d->debug;
   kp.out[0] = d->out[0]; kp.out[1] = d->out[1]; kp.out[2] = d->out[2];
   kp.row_scale = d->row_scale; kp.ldc = d->ldc; kp.status = d->status;
   kp.timeout_ns = (unsigned long long)(d->timeout_ns > 0 ? d->timeout_ns : 2000000000ll);
@@ -503,6 +582,13 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
     if ((rc = make_map(&kp.b[0][0], d->b[0][0], d->a_rows, d->N, d->ldb, 64, BK))) return rc;
     kp.a[1] = kp.a[0]; kp.b[0][1] = kp.b[1][0] = kp.b[1][1] = kp.b[0][0];
     if (d->epi != EPI_F32) return fail(-3, "wgrad writes fp32");
+    const int n_local = d->split < d->ngroups ? d->split : d->ngroups;
+    if ((rc = make_map_f32(&kp.c[0], d->out[0], (int64_t)n_local * d->Mw, d->N, d->ldc))) return rc;
+    kp.c[1] = kp.c[0];
+    if (d->ngroups > d->split) {
+      if (d->out[1] == nullptr) return fail(-8, "wgrad: groups >= split need a slot grad tensor");
+      if ((rc = make_map_f32(&kp.c[1], d->out[1], (int64_t)(d->ngroups - d->split) * d->Mw, d->N, d->ldc))) return rc;
+    }
     return launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
   }
   // A reduction tail is legal: the TMA loads zero-fill A beyond K, which also cancels whatever

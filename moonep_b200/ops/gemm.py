@@ -40,7 +40,7 @@ class _GemmDesc(ctypes.Structure):
         ("total_rows", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
         ("rows_per_expert", ctypes.c_int32), ("Mw", ctypes.c_int32),
         ("accumulate", ctypes.c_int32), ("zero_empty_below", ctypes.c_int32),
-        ("grid", ctypes.c_int32),
+        ("grid", ctypes.c_int32), ("debug", ctypes.c_int32), ("pad_", ctypes.c_int32),
         ("a_rows", ctypes.c_int64), ("lda", ctypes.c_int64 * 2), ("a", ctypes.c_void_p * 2),
         ("b", (ctypes.c_void_p * 2) * 2), ("b_rows", ctypes.c_int64 * 2), ("ldb", ctypes.c_int64),
         ("cu_seqlens", ctypes.c_void_p), ("out", ctypes.c_void_p * 3), ("ldc", ctypes.c_int64),
@@ -69,8 +69,12 @@ def check_status(device="cuda") -> None:
         raise RuntimeError(f"grouped GEMM: bounded wait expired (code {st[0]}, where {st[2]}, CTA {st[3]})")
 
 
+DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
+
+
 def _launch(d: _GemmDesc) -> None:
     global _checked_layout
+    d.debug = DEBUG_MODE
     if not _checked_layout:
         assert nat.call("mep_gemm_desc_bytes") == ctypes.sizeof(_GemmDesc), "GemmDesc layout mismatch"
         _checked_layout = True
