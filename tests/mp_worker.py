@@ -170,6 +170,39 @@ def layer_check(R, rank):
     buf.destroy()
 
 
+def decoder_check(R, rank):
+    """The fused EP path and the NCCL all-to-all path are two implementations of the same model:
+    with identical parameters their first loss agrees, and both train."""
+    from moonep_b200.models.decoder import MoEDecoder, NcclMoELayer
+    from moonep_b200.models.moe_layer import ExpertPools, MoELayer
+    S, Hd, K, Hp, V = 256, 256, 4, 128, 211
+    E = 4 * R
+    g = torch.Generator(device="cuda").manual_seed(7 + rank)
+    tok = torch.randint(0, V, (S,), device="cuda", generator=g)
+    tgt = torch.randint(0, V, (S,), device="cuda", generator=g)
+    bias = torch.zeros(E, device="cuda")
+    bias[: E // R] = 1.0
+    out = {}
+    for impl in ("fused", "nccl"):
+        torch.manual_seed(3)
+        if impl == "fused":
+            buf = Buffer(S, Hd, K, E, R, num_sms=8, token_padding=64, timeout_s=10.0)
+            pools = ExpertPools(R, E // R, Hd, Hp, buf.group, rank)
+            fac = lambda i: MoELayer(buf, Hp, pools, seed=20 + i, init_std=0.05, router_bias=bias)
+        else:
+            fac = lambda i: NcclMoELayer(S, Hd, K, E, Hp, seed=20 + i, init_std=0.05, router_bias=bias,
+                                         token_padding=64)
+        model = MoEDecoder(V, Hd, 2, 4, fac).cuda()
+        out[impl] = [float(model.train_step(tok, tgt, 0.05)) for _ in range(4)]
+        if impl == "fused":
+            buf.check()
+            buf.destroy()
+    all_ok(abs(out["fused"][0] - out["nccl"][0]) < 2e-2, "fused vs nccl first loss", str(out))
+    all_ok(out["fused"][-1] < out["fused"][0] and out["nccl"][-1] < out["nccl"][0], "both train", str(out))
+    if rank == 0:
+        print(f"decoder R={R}: {out}", flush=True)
+
+
 def _all_gather(t, R):
     lst = [torch.empty_like(t) for _ in range(R)]
     dist.all_gather(lst, t.contiguous())
@@ -186,6 +219,8 @@ def main():
         comm_checks(R, rank)
     if what in ("all", "layer"):
         layer_check(R, rank)
+    if what in ("all", "decoder"):
+        decoder_check(R, rank)
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK R={R} {what}", flush=True)
