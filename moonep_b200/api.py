@@ -48,7 +48,7 @@ nat.declare("mep_launch_expand", I, [P, P, P, P])
 nat.declare("mep_launch_combine_prologue", I, [P, P, P, P])
 nat.declare("mep_launch_combine", I, [P, P, P, P, P])
 nat.declare("mep_launch_prefetch", I, [P, P, I, P, P, P, P, P])
-nat.declare("mep_launch_grad_reduce", I, [P, P, I, P, P, P, P, I, P])
+nat.declare("mep_launch_grad_reduce", I, [P, P, I, P, P, P, P, I, I, P])
 nat.declare("mep_launch_sync", I, [P, P])
 
 _KERNEL_NAMES = {1: "sync", 2: "plan", 3: "dispatch", 4: "expand", 5: "combine_prologue",
@@ -481,13 +481,15 @@ class Buffer:
     def reduce_grad(self, plan: CommPlan, async_finish: bool = False, *,
                     local_gate_grad, local_up_grad, local_down_grad,
                     gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer,
-                    entry_sync: bool = True):
+                    entry_sync: bool = True, zero_consumed: bool = True):
         """Home ranks pull the fp32 prefetch-slot grads of their experts from every rank's
         ``[R, epn, ...]`` reduce buffer, add them to the local grad in ascending (rank, slot)
         order, then every rank zeroes its consumed slots (moonep/api.py:1106-1193).
 
         ``entry_sync=True`` adds a cross-rank barrier first, so that the grads other ranks wrote
-        on their streams before calling are visible; the reference leaves that to the caller."""
+        on their streams before calling are visible; the reference leaves that to the caller.
+        ``zero_consumed=False`` skips the final clearing for callers whose next backward pass
+        overwrites the slots instead of accumulating into them."""
         self._require()
         assert plan is not None, "plan is required"
         locals_ = [local_gate_grad, local_up_grad, local_down_grad]
@@ -500,7 +502,7 @@ class Buffer:
 
         def run():
             self._rc(nat.call("mep_launch_grad_reduce", self._ctx, plan.experts_to_copy.data_ptr(), n,
-                              lp, pp, eb, rs, int(entry_sync), self._stream()), "reduce_grad")
+                              lp, pp, eb, rs, int(entry_sync), int(zero_consumed), self._stream()), "reduce_grad")
             self._stats["reduce_grad"] += 1
             self._maybe_check()
 

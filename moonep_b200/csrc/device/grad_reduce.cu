@@ -26,7 +26,7 @@ constexpr int GR_VEC_PER_THREAD = GR_CHUNK / 16 / GR_ACC_THREADS;  // 8 float4 p
 
 struct GradReduceParams {
   SyncCtx sync;
-  int epn, n_tensors, entry_barrier;
+  int epn, n_tensors, entry_barrier, zero_consumed;
   const int32_t* etc;                     // [Rv][R*epn]
   float* local[GR_MAX_TENSORS];           // [Rv][epn][expert_elems]
   float* pool[GR_MAX_TENSORS];            // slot (d,b) at pool + d*rank_stride + b*expert_elems
@@ -180,15 +180,31 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
   }
   // every home rank has read what it needs before anyone clears
   cross_rank_barrier(sc, 2);
-  for (int b = 0; b < epn; ++b) {
-    if (etc[rank * epn + b] < 0) continue;
-    for (int t = 0; t < p.n_tensors; ++t) {
-      float4* z = reinterpret_cast<float4*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
-                                            (size_t)b * p.expert_elems[t]);
-      const int64_t nv = p.expert_elems[t] / 4;
-      for (int64_t v = (int64_t)c * GR_THREADS + tid; v < nv; v += (int64_t)G * GR_THREADS)
-        z[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!p.zero_consumed) return;
+  // clear my consumed slots: bulk stores of a zeroed ring stage, many in flight per CTA
+  for (uint32_t i = tid * 16u; i < GR_CHUNK; i += GR_THREADS * 16u)
+    *reinterpret_cast<uint4*>(ring + i) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0) {
+    int pending = 0;
+    int64_t seq = 0;
+    for (int b = 0; b < epn; ++b) {
+      if (etc[rank * epn + b] < 0) continue;
+      for (int t = 0; t < p.n_tensors; ++t) {
+        uint8_t* z = reinterpret_cast<uint8_t*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
+                                                (size_t)b * p.expert_elems[t]);
+        const int64_t bytes = p.expert_elems[t] * 4;
+        for (int64_t off = 0; off < bytes; off += GR_CHUNK, ++seq) {
+          if (seq % G != c) continue;
+          const int64_t rem = bytes - off;
+          bulk_s2g(z + off, ring, (uint32_t)(rem < (int64_t)GR_CHUNK ? rem : (int64_t)GR_CHUNK));
+          if (++pending == 32) { bulk_commit(); bulk_wait_read<2>(); pending = 0; }
+        }
+      }
     }
+    bulk_commit();
+    bulk_wait<0>();
   }
 }
 
@@ -223,12 +239,14 @@ extern "C" {
 // (multiple of 4), element stride between ranks' pools.
 int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* const* local,
                            void* const* pool, const int64_t* expert_elems,
-                           const int64_t* rank_stride, int entry_barrier, cudaStream_t stream) {
+                           const int64_t* rank_stride, int entry_barrier, int zero_consumed,
+                           cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (n < 1 || n > GR_MAX_TENSORS) return fail(-1, "reduce_grad: %d tensors (1..%d)", n, GR_MAX_TENSORS);
   GradReduceParams p;
   p.sync = c.sync(KID_REDUCE);
   p.epn = c.epn; p.n_tensors = n; p.etc = etc; p.entry_barrier = entry_barrier;
+  p.zero_consumed = zero_consumed;
   for (int t = 0; t < n; ++t) {
     if (expert_elems[t] % 4 != 0 || rank_stride[t] % 4 != 0 ||
         ((uintptr_t)local[t] | (uintptr_t)pool[t]) % 16 != 0)

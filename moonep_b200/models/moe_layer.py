@@ -119,7 +119,8 @@ class _MoEFn(torch.autograd.Function):
         if have_slots and pools.reduce:
             buf.reduce_grad(plan, local_gate_grad=layer.g_gate, local_up_grad=layer.g_up,
                             local_down_grad=layer.g_down, gate_reduce_buffer=pools.reduce["gate"],
-                            up_reduce_buffer=pools.reduce["up"], down_reduce_buffer=pools.reduce["down"])
+                            up_reduce_buffer=pools.reduce["up"], down_reduce_buffer=pools.reduce["down"],
+                            zero_consumed=layer.accumulate_grads)   # overwritten next step otherwise
         # router backward
         d_logits = ew.router_topk_bwd(w, dw_sk, topk, buf.E)                 # [S, E] bf16
         gemm.wgrad(x, d_logits, None, layer.g_router, accumulate=acc)

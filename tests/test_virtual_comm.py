@@ -161,3 +161,35 @@ def test_barrier_many_rounds_and_sync_kernel():
         buf.inter_rank_sync()
     buf.check()
     assert buf.sync_state[:, 1].tolist() == [2000] * 8
+
+
+def test_bounded_wait_reports_status_and_recovers():
+    """Failure detection without a GPU fault: one virtual rank is made to expect a barrier epoch
+    that its peer will never publish (a flag that nothing sets).  Its wait runs out after the
+    short limit, the kernel RETURNS, the host reads the status block and raises; after
+    ``reset_barriers()`` the same Buffer works again."""
+    from moonep_b200 import Buffer
+    from moonep_b200.api import CommTimeoutError
+    buf = Buffer(8, 64, 2, 4, 2, num_sms=1, token_padding=8, virtual=True, timeout_s=0.2)
+    buf.inter_rank_sync()
+    buf.check()
+    buf.sync_state[0, 1] += 5            # rank 0 now waits for an epoch rank 1 never reaches
+    torch.cuda.synchronize()
+    buf.inter_rank_sync()
+    with pytest.raises(CommTimeoutError) as exc:
+        buf.check()
+    info = exc.value.info
+    assert info["kernel"] == "sync" and info["code"] == 2 and info["rank"] == 0 and info["peer"] == 1
+    assert info["expected"] - info["observed"] == 5
+    buf.reset_barriers()
+    for _ in range(3):
+        buf.inter_rank_sync()
+    buf.check()
+    # and a full round trip still works on the recovered Buffer
+    x = torch.randn(2, 8, 64, device="cuda").bfloat16()
+    topk = torch.tensor([[0, 1]] * 8 + [[2, 3]] * 8, dtype=torch.int32, device="cuda").view(2, 8, 2)
+    tpe = torch.stack([torch.bincount(topk[r].flatten().long(), minlength=4) for r in range(2)]).to(torch.int32)
+    h, _, _, plan = buf.dispatch(x, None, topk, tpe)
+    out, _, _ = buf.combine(plan, h)
+    buf.check()
+    assert torch.equal(out.float(), (x.float() * 2).bfloat16().float())
