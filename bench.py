@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--maxvio", type=float, default=2.0, help="target routing imbalance")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--small", action="store_true", help="reduced shape for profiling captures (not a bench)")
+    ap.add_argument("--experts", type=int, default=E,
+                    help="total experts; anything but 256 is a profiling shape, not the benchmark")
     return ap.parse_args()
 
 
@@ -103,9 +105,10 @@ def calibrate_bias(layer, x, target, dist, R):
         return None, 0.0
     dev = x.device
     g = torch.Generator().manual_seed(1234)
-    order = torch.randperm(E, generator=g)
-    ranks = torch.empty(E)
-    ranks[order] = torch.arange(1, E + 1, dtype=torch.float32)
+    n_exp = layer.w_router.shape[1]
+    order = torch.randperm(n_exp, generator=g)
+    ranks = torch.empty(n_exp)
+    ranks[order] = torch.arange(1, n_exp + 1, dtype=torch.float32)
     logpop = -torch.log(ranks).to(dev)
     logits = gemm.dense(x, layer.w_router)
     lo, hi, best = 0.0, 8.0, (None, 1e9)
@@ -142,7 +145,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if R > 1:
         dist.init_process_group("nccl", device_id=dev)
-    s, h, hp, k, e = (512, 1024, 512, 4, 32) if args.small else (S, H, HP, K, E)
+    s, h, hp, k, e = (512, 1024, 512, 4, 32) if args.small else (S, H, HP, K, args.experts)
     buf = Buffer(s, h, k, e, R, num_sms=NUM_SMS if R > 1 else 16, token_padding=TOKEN_PADDING)
     pools = ExpertPools(R, e // R, h, hp, buf.group, rank) if R > 1 else None
     layer = MoELayer(buf, hp, pools, seed=0)
@@ -257,7 +260,7 @@ def run_ours(args):
         "data": "synthetic (N(0,1) tokens, random-init weights, Zipf router bias)",
         "impl": "ours",
         "config": {"model": "deepseek-v3-style MoE layer: router 7168->256 top-8 softmax, 256 SwiGLU experts H=7168 H'=2048"
-                   if not args.small else "small profiling shape",
+                   if not args.small and args.experts == E else f"profiling shape (experts={e})",
                    "global_batch": tokens, "seq_len": s, "parallelism": f"ep{R}",
                    "tokens_per_rank": s, "token_padding": TOKEN_PADDING, "num_sms_comm": buf.num_sms,
                    "maxvio_target": args.maxvio, "maxvio_achieved": mv,
