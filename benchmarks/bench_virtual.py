@@ -34,6 +34,11 @@ def main():
     topk, w = topk.cuda(), w.cuda()
     x = torch.randn(a.R, a.S, a.H, device="cuda").bfloat16()
     res = {}
+    h, _, _, plan = buf.dispatch(x, w, topk, tpe, zero_copy=True, router_weights_zero_copy=True)
+    out, _, _ = buf.combine(plan, h, None, zero_copy=True)
+    ref = (x.float() * a.K).bfloat16().float()
+    res["identity_max_err"] = float((out.float() - ref).abs().max())
+    # timing loops below re-run combine on an already pre-reduced shard: times only, no checks
     for name in ("dispatch", "combine"):
         ts = []
         for _ in range(a.iters + 1):
@@ -50,8 +55,6 @@ def main():
             ts.append(s.elapsed_time(e) * 1e3)
         res[name + "_us"] = round(min(ts[1:]), 1)
     buf.check()
-    ref = (x.float() * a.K).bfloat16().float()
-    res["identity_max_err"] = float((out.float() - ref).abs().max())
     res.update(R=a.R, S=a.S, H=a.H, K=a.K, E=a.E, maxvio=round(mv, 2), rows_per_rank=int(plan.cu_seqlens[0, -1]))
     print(json.dumps(res))
     buf.destroy()
