@@ -118,7 +118,7 @@ def main():
             plan.remote_stats.data_ptr(), stream()), nat.call("mep_launch_sync", buf._ctx, stream())))
         row["k_dispatch_us"] = timed(lambda: nat.call(
             "mep_launch_dispatch", buf._ctx, x.data_ptr(), 0, plan.dst.data_ptr(),
-            plan.zero_fill_ranges.data_ptr(), 0, 1, 0, stream()))
+            plan.zero_fill_ranges.data_ptr(), 0, 0, 1, 0, stream()))
         row["k_expand_us"] = timed(lambda: nat.call(
             "mep_launch_expand", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), stream()))
         row["k_prologue_us"] = timed(lambda: nat.call(

@@ -43,7 +43,8 @@ nat.declare("mep_meta_offsets", None, [L, I, I, ctypes.POINTER(ctypes.c_int64)])
 nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
 nat.declare("mep_ctx_destroy", None, [P])
 nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P])
-nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, I, I, P])
+nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, P, I, I, P])
+nat.declare("mep_launch_push_reduce", I, [P, P, L, P, L, P, P, P, P, P, I, P])
 nat.declare("mep_launch_expand", I, [P, P, P, P])
 nat.declare("mep_launch_combine_prologue", I, [P, P, P, P])
 nat.declare("mep_launch_combine", I, [P, P, P, P, P])
@@ -148,9 +149,10 @@ class Buffer:
                 (meta_ints,), torch.int32, group=self.group, device=self.device)
         self.hidden_stride = self.hidden_buf.shape[0] // R
         self.meta_stride = self.meta_buf.shape[0] // R
-        offs = (ctypes.c_int64 * 5)()
+        offs = (ctypes.c_int64 * 6)()
         nat.call("mep_meta_offsets", self.NvS, R, E, offs)
-        self.weights_off, self.link_off, self.tpe_off, self.flags_off, self.arrive_off = list(offs)
+        (self.weights_off, self.link_off, self.tpe_off, self.flags_off, self.arrive_off,
+         self.src_off) = list(offs)
         # every rank zeroes ITS OWN chunk, then the group meets: flags start at epoch 0
         if self.virtual:
             self.meta_buf.zero_()
@@ -330,16 +332,18 @@ class Buffer:
             etc = torch.empty(self._shape(self.R, self.epn), **i32)
             rs = torch.empty(self._shape(2), **i32)
             link = torch.empty(self._shape(self.NvS), **i32)
+            src = torch.empty(self._shape(self.NvS), **i32)
             self._rc(nat.call("mep_launch_plan", self._ctx, topk.data_ptr(), tpe.data_ptr(),
                               dst.data_ptr(), cu.data_ptr(), zf.data_ptr(), etc.data_ptr(),
                               rs.data_ptr(), st), "plan")
             plan = CommPlan(dst=dst, experts_to_copy=etc, zero_fill_ranges=zf, remote_stats=rs,
                             cu_seqlens=cu, link=link, N=self.N, R=self.R, E=self.E, NvS=self.NvS,
-                            K=self.K)
+                            K=self.K, src_info=src)
             self._last_plan = plan
         self._rc(nat.call("mep_launch_dispatch", self._ctx, x.data_ptr(), nat.ptr(w),
                           plan.dst.data_ptr(), plan.zero_fill_ranges.data_ptr(),
                           plan.link.data_ptr() if fresh else 0,
+                          plan.src_info.data_ptr() if fresh else 0,
                           int(bool(inter_rank_sync) and not fresh), int(fresh), st), "dispatch")
         self._rc(nat.call("mep_launch_expand", self._ctx, plan.link.data_ptr(),
                           plan.cu_seqlens.data_ptr(), st), "dispatch expand")
@@ -410,6 +414,53 @@ class Buffer:
                           nat.ptr(w_out), st), "combine")
         self._stats["combine"] += 1
         self._stats["bytes_combine"] += self.N * self.H * 2 * self.Rv
+        self._maybe_check()
+        return out, w_out
+
+    # ---- pushed combine (GEMM fused with the combine all-to-all) ---------------------------------
+    def enable_push(self) -> None:
+        """Allocate the symmetric staging buffers of the pushed combine: ``[R, S*K, H]`` bf16 rows
+        and ``[R, S*K]`` fp32 scalars.  Collective (every rank must call it)."""
+        self._require()
+        if getattr(self, "push_buf", None) is not None:
+            return
+        if self._solo:
+            self.push_buf = symm.create_local_group_tensor((self.N, self.H), torch.bfloat16, self.R, self.device)
+            self.wpush_buf = symm.create_local_group_tensor((self.N,), torch.float32, self.R, self.device)
+        else:
+            self.push_buf = symm.create_nvl_dist_tensor((self.N, self.H), torch.bfloat16, group=self.group, device=self.device)
+            self.wpush_buf = symm.create_nvl_dist_tensor((self.N,), torch.float32, group=self.group, device=self.device)
+        self.push_stride = self.push_buf.shape[0] // self.R * self.H       # elements per rank
+        self.wpush_stride = self.wpush_buf.shape[0] // self.R
+
+    def push_target(self, plan: CommPlan) -> dict:
+        """Arguments the GEMM's push epilogue needs to send each row of this rank's shard to the
+        staging slot of its (token, k) entry on the token's home rank."""
+        self.enable_push()
+        assert plan.src_info is not None, "plan has no source records"
+        return dict(src_info=plan.src_info, push_base=self.push_buf, push_rank_stride=self.push_stride,
+                    push_entries=self.N, push_ranks=self.R)
+
+    def combine_pushed(self, plan: CommPlan, row_scalar: Optional[torch.Tensor] = None):
+        """Finish a combine whose rows were pushed home by the producing GEMM's epilogue: one
+        cross-rank barrier, then the local K-way fp32 sum.  ``row_scalar`` ([NvS] fp32, e.g. the
+        route-weight grads) is sent home too and returned as ``[S, K]``.
+        Returns ``(hidden_sh[S,H], scalars_sk[S,K] | None)``."""
+        self._require()
+        self.enable_push()
+        dev = self.push_buf.device
+        out = torch.empty(self._shape(self.S, self.H), dtype=torch.bfloat16, device=dev)
+        w_out = None
+        if row_scalar is not None:
+            assert row_scalar.dtype == torch.float32 and tuple(row_scalar.shape) == self._shape(self.NvS)
+            assert row_scalar.is_contiguous()
+            w_out = torch.empty(self._shape(self.S, self.K), dtype=torch.float32, device=dev)
+        grid_x = self.num_sms if self.virtual else self.num_sms_local
+        self._rc(nat.call("mep_launch_push_reduce", self._ctx, self.push_buf.data_ptr(), self.push_stride,
+                          self.wpush_buf.data_ptr(), self.wpush_stride, plan.src_info.data_ptr(),
+                          nat.ptr(row_scalar), plan.cu_seqlens.data_ptr(), out.data_ptr(),
+                          nat.ptr(w_out), grid_x, self._stream()), "combine_pushed")
+        self._stats["combine"] += 1
         self._maybe_check()
         return out, w_out
 
@@ -543,7 +594,7 @@ class Buffer:
         finally:
             nat.call("mep_ctx_destroy", self._ctx)
             self._ctx = None
-            for name in ("meta_mc", "meta_buf", "hidden_buf"):
+            for name in ("meta_mc", "meta_buf", "hidden_buf", "push_buf", "wpush_buf"):
                 t = getattr(self, name, None)
                 setattr(self, name, None)
                 if t is not None:

@@ -45,8 +45,11 @@ MEP_HD int64_t nvs_rows(int64_t S, int64_t K, int64_t epn, int64_t token_padding
 //   TPE      [2][R][E]    gathered tokens-per-expert, double buffered by plan parity
 //   FLAGS    [R]          barrier arrival epochs, slot p is written by rank p
 //   ARRIVE   [NvS/128+1]  per-128-row tile arrival counters (fused dispatch->GEMM path)
+//   SRC      [NvS]        per slot: source_rank * (S*K) + (token*K + k) of the entry that owns
+//                         it, written by the source ranks' planners (-1 on padding rows); the
+//                         GEMM epilogue that pushes results home reads it
 struct MetaLayout {
-  int64_t weights_off, link_off, tpe_off, flags_off, arrive_off, total;
+  int64_t weights_off, link_off, tpe_off, flags_off, arrive_off, src_off, total;
 };
 MEP_HD MetaLayout meta_layout(int64_t NvS, int64_t R, int64_t E) {
   MetaLayout m;
@@ -55,7 +58,8 @@ MEP_HD MetaLayout meta_layout(int64_t NvS, int64_t R, int64_t E) {
   m.tpe_off = m.link_off + align_up64(NvS, 4);
   m.flags_off = m.tpe_off + align_up64(2 * R * E, 4);
   m.arrive_off = m.flags_off + align_up64(R, 32);
-  m.total = m.arrive_off + align_up64(NvS / 128 + 1, 32);
+  m.src_off = m.arrive_off + align_up64(NvS / 128 + 1, 32);
+  m.total = m.src_off + align_up64(NvS, 4);
   return m;
 }
 

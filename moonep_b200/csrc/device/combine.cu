@@ -244,6 +244,79 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
   }
 }
 
+// ---- pushed combine: barrier, then every rank sums the K rows its peers pushed per token -------
+// Counterpart of the pull combine for the fused path: the GEMM epilogue (grouped_gemm.cu, PUSH)
+// already stored every result row into staging[home rank][token*K + k], so what is left is one
+// cross-rank barrier and a local, bandwidth-bound K-way fp32 sum in ascending k.  Route-weight
+// grads (backward of dispatch) ride along: each rank first pushes its per-row scalars to the
+// owners' fp32 staging, the owners read them back after the barrier.
+struct PushReduceParams {
+  SyncCtx sync;
+  int S, K, H, epn;
+  int64_t N, NvS, push_stride, wpush_stride;
+  const __nv_bfloat16* push;       // symmetric [R][N][H]
+  float* wpush;                    // symmetric [R][N]
+  const int32_t* src_info;         // [Rv][NvS]
+  const float* row_scalar;         // [Rv][NvS] or null
+  const int32_t* cu_seqlens;       // [Rv][2epn]
+  __nv_bfloat16* out;              // [Rv][S][H]
+  float* w_out;                    // [Rv][S][K] or null
+};
+
+constexpr int PUSH_REDUCE_THREADS = 256;
+
+__global__ void __launch_bounds__(PUSH_REDUCE_THREADS, 1) ep_push_reduce_kernel(const PushReduceParams p) {
+  const SyncCtx& sc = p.sync;
+  const int tid = threadIdx.x;
+  const int vr = blockIdx.y, rank = sc.rank_base + vr;
+  const int G = gridDim.x, c = blockIdx.x;
+  if (p.row_scalar != nullptr) {
+    const int32_t* si = p.src_info + (size_t)vr * p.NvS;
+    const float* rs = p.row_scalar + (size_t)vr * p.NvS;
+    int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
+    if (rows > p.NvS) rows = p.NvS;
+    for (int64_t r = (int64_t)c * PUSH_REDUCE_THREADS + tid; r < rows; r += (int64_t)G * PUSH_REDUCE_THREADS) {
+      const int v = si[r];
+      if (v < 0) continue;
+      const int64_t sr = v / p.N, ent = v - sr * p.N;
+      if (sr < sc.R) p.wpush[(size_t)sr * p.wpush_stride + ent] = rs[r];
+    }
+  }
+  fence_sys();
+  cross_rank_barrier(sc, 1);
+  const uint4* mine = reinterpret_cast<const uint4*>(p.push + (size_t)rank * p.push_stride);
+  uint4* out = reinterpret_cast<uint4*>(p.out + (size_t)vr * p.S * p.H);
+  const int nvec = p.H / 8;
+  for (int s = c; s < p.S; s += G) {
+    const uint4* base = mine + (size_t)s * p.K * nvec;
+    for (int v = tid; v < nvec; v += PUSH_REDUCE_THREADS) {
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+      for (int k0 = 0; k0 < p.K; k0 += 8) {
+        uint4 raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          raw[u] = k0 + u < p.K ? base[(size_t)(k0 + u) * nvec + v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          float t[8];
+          bf16x8_to_f32(raw[u], t);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[q] += t[q];
+        }
+      }
+      out[(size_t)s * nvec + v] = f32_to_bf16x8(acc);
+    }
+  }
+  if (p.w_out != nullptr) {
+    const float* wm = p.wpush + (size_t)rank * p.wpush_stride;
+    float* wo = p.w_out + (size_t)vr * p.N;
+    for (int64_t i = (int64_t)c * PUSH_REDUCE_THREADS + tid; i < p.N; i += (int64_t)G * PUSH_REDUCE_THREADS)
+      wo[i] = wm[i];
+  }
+}
+
 template <int ST, int NV>
 static int launch_combine_t(const BufferCtx& c, CombineParams& p, size_t smem, cudaStream_t stream) {
   static thread_local size_t configured = 0;
@@ -286,6 +359,25 @@ int mep_launch_combine_prologue(const void* ctx_, const int32_t* link, const int
   dim3 grid(c.num_sms_local * 6, c.Rv());
   ep_combine_prologue_kernel<<<grid, PROLOGUE_THREADS, 0, stream>>>(p);
   MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Finish a pushed combine: push [R][push_stride] bf16 rows / wpush [R][wpush_stride] fp32 scalars
+// are the symmetric staging buffers; row_scalar (may be null) is this rank's per-row scalar to
+// send home (route-weight grads); out [Rv][S][H], w_out [Rv][S][K] or null.
+int mep_launch_push_reduce(const void* ctx_, const void* push, int64_t push_stride, void* wpush,
+                           int64_t wpush_stride, const int32_t* src_info, const float* row_scalar,
+                           const int32_t* cu_seqlens, void* out, float* w_out, int grid_x,
+                           cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  PushReduceParams p;
+  p.sync = c.sync(KID_COMBINE);
+  p.S = c.S; p.K = c.K; p.H = c.H; p.epn = c.epn; p.N = c.N; p.NvS = c.NvS;
+  p.push_stride = push_stride; p.wpush_stride = wpush_stride;
+  p.push = (const __nv_bfloat16*)push; p.wpush = (float*)wpush; p.src_info = src_info;
+  p.row_scalar = row_scalar; p.cu_seqlens = cu_seqlens; p.out = (__nv_bfloat16*)out; p.w_out = w_out;
+  dim3 grid(grid_x > 0 ? grid_x : c.num_sms, c.Rv());
+  MEP_CUDA_OK(launch_coop((const void*)ep_push_reduce_kernel, grid, dim3(PUSH_REDUCE_THREADS), 0, stream, p));
   return 0;
 }
 

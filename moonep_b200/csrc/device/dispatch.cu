@@ -25,13 +25,14 @@ namespace mep {
 struct DispatchParams {
   SyncCtx sync;
   int S, K, H, epn;
-  int64_t N, NvS, hidden_stride, weights_off, link_off;
+  int64_t N, NvS, hidden_stride, weights_off, link_off, src_off;
   const __nv_bfloat16* x;     // [Rv][S][H]
   const float* w;             // [Rv][S][K] or null
   const int32_t* dst;         // [Rv][N]
   const int32_t* zero_fill;   // [Rv][2epn][2]
   __nv_bfloat16* hidden;      // symmetric, chunk of rank 0
   int32_t* link_out;          // [Rv][NvS] or null
+  int32_t* src_out;           // [Rv][NvS] or null
   int entry_barrier;
   int fresh;                  // plan made by the preceding planner launch
 };
@@ -139,7 +140,7 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
       } else {
         for (int r = first + c * 32 + lane; r < first + n; r += G * 32) {
           if (p.w != nullptr) my_meta[p.weights_off + r] = 0;
-          if (p.fresh) my_meta[p.link_off + r] = LINK_NONE;
+          if (p.fresh) { my_meta[p.link_off + r] = LINK_NONE; my_meta[p.src_off + r] = -1; }
         }
       }
     }
@@ -151,6 +152,12 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
   if (p.link_out != nullptr) {
     const int32_t* src = sc.meta + (size_t)rank * sc.meta_stride + p.link_off;
     int32_t* out = p.link_out + (size_t)vr * p.NvS;
+    for (int64_t i = (int64_t)c * DISPATCH_THREADS + tid; i < p.NvS; i += (int64_t)G * DISPATCH_THREADS)
+      out[i] = src[i];
+  }
+  if (p.src_out != nullptr) {
+    const int32_t* src = sc.meta + (size_t)rank * sc.meta_stride + p.src_off;
+    int32_t* out = p.src_out + (size_t)vr * p.NvS;
     for (int64_t i = (int64_t)c * DISPATCH_THREADS + tid; i < p.NvS; i += (int64_t)G * DISPATCH_THREADS)
       out[i] = src[i];
   }
@@ -220,17 +227,17 @@ extern "C" {
 // link_out [Rv][NvS] or null.  fresh != 0: the plan comes from the planner launch that
 // precedes this one on the stream (its barrier stands in for the entry sync).
 int mep_launch_dispatch(const void* ctx_, const void* x, const float* w, const int32_t* dst,
-                        const int32_t* zero_fill, int32_t* link_out, int entry_barrier, int fresh,
-                        cudaStream_t stream) {
+                        const int32_t* zero_fill, int32_t* link_out, int32_t* src_out, int entry_barrier,
+                        int fresh, cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (c.H % 8 != 0) return fail(-1, "dispatch needs H %% 8 == 0 (got %d)", c.H);
   DispatchParams p;
   p.sync = c.sync(KID_DISPATCH);
   p.S = c.S; p.K = c.K; p.H = c.H; p.epn = c.epn;
   p.N = c.N; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
-  p.weights_off = c.ml.weights_off; p.link_off = c.ml.link_off;
+  p.weights_off = c.ml.weights_off; p.link_off = c.ml.link_off; p.src_off = c.ml.src_off;
   p.x = (const __nv_bfloat16*)x; p.w = w; p.dst = dst; p.zero_fill = zero_fill;
-  p.hidden = (__nv_bfloat16*)c.hidden; p.link_out = link_out;
+  p.hidden = (__nv_bfloat16*)c.hidden; p.link_out = link_out; p.src_out = src_out;
   p.entry_barrier = entry_barrier; p.fresh = fresh;
   const size_t row = (size_t)c.H * 2;
   // virtual groups must keep gridDim.x * R CTAs co-resident: leave room for 2 CTAs per SM

@@ -16,6 +16,10 @@
 //        epilogues: bf16 store, fp32 store, or SwiGLU: the tile holds 128 gate and 128 up
 //        columns of the same output columns; writes gate, up and silu(gate)*up*row_scale.
 //        Up to two K segments accumulate into one tile (dX = dG*Wg^T + dU*Wu^T).
+//        PUSH epilogue (GEMM fused with the combine all-to-all): each finished row segment is
+//        stored, over NVLink, straight into the slot of its (token, k) entry in the token's
+//        HOME rank's staging buffer, so the transfer overlaps the math tile by tile; the home
+//        rank then only sums K local rows per token.
 //   weight-grad (groups partition the REDUCTION dimension):
 //        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output.
 // Group g < split reads/writes allocation 0 (local experts), g >= split allocation 1 (this
@@ -41,7 +45,7 @@ constexpr int GEMM_THREADS = 192;
 constexpr int MAX_GROUPS = 1024;
 constexpr int GEMM_SMEM = GEMM_STAGES * STAGE_BYTES + 1024;
 
-enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2, EPI_PUSH = 3 };
 
 struct GemmKParams {
   CUtensorMap a[2];
@@ -55,6 +59,11 @@ struct GemmKParams {
   long long ldc;
   int32_t* status;
   unsigned long long timeout_ns;
+  // EPI_PUSH: results go straight to the token's home rank (see the epilogue)
+  const int32_t* src_info;
+  void* push_base;
+  long long push_rank_stride;
+  int push_entries, push_ranks;
 };
 
 struct Tile {
@@ -139,6 +148,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ int s_end[MAX_GROUPS];
   __shared__ int s_prefix[MAX_GROUPS + 1];
   __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];   // per-warp staging pad
+  __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -340,6 +350,54 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             }
           }
         }
+      } else if constexpr (EPI == EPI_PUSH) {
+        // thread = output row.  The row's owner entry (source rank, token*K+k) comes from the
+        // per-slot source record; padding rows have none and are dropped.  64 columns at a time
+        // are staged in a swizzled per-warp pad and leave as full 128-byte lines: every store
+        // instruction covers 4 rows x 128 B, 8 lanes per row, addressed at the home rank.
+        uint8_t* pad = s_push + q * 4096;
+        const bool row_ok = r_in_tile < t.rows;
+        const long long row = (long long)t.row0 + r_in_tile;
+        const int si = row_ok ? p.src_info[row] : -1;
+        unsigned long long dptr = 0ull;
+        if (si >= 0) {
+          const int sr = si / p.push_entries, ent = si - sr * p.push_entries;
+          if (sr < p.push_ranks)
+            dptr = (unsigned long long)((__nv_bfloat16*)p.push_base + (long long)sr * p.push_rank_stride +
+                                        (long long)ent * p.ldc + t.n0);
+        }
+#pragma unroll 1
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(tacc + c2 * 64, ra);
+          tmem_ld_32x32(tacc + c2 * 64 + 32, rb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t* src = j < 4 ? ra + 8 * j : rb + 8 * (j - 4);
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1]));
+              pk[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(pad + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+          __syncwarp();
+          const int j = lane & 7;
+          const bool col_ok = t.n0 + c2 * 64 + j * 8 < p.N;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int rr = g * 4 + (lane >> 3);
+            const unsigned long long pr = __shfl_sync(0xffffffffu, dptr, rr);
+            const uint4 v = *reinterpret_cast<const uint4*>(pad + rr * 128 + ((j ^ (rr & 7)) << 4));
+            if (pr != 0ull && col_ok)
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(pr) + c2 * 64 + j * 8) = v;
+          }
+          __syncwarp();
+        }
+        __threadfence_system();   // pushed rows are ordered before this rank's next barrier arrival
       } else {
         bool row_ok;
         long long off_row;
@@ -495,6 +553,10 @@ struct GemmDesc {
   const float* row_scale;
   int32_t* status;
   int64_t timeout_ns;
+  const int32_t* src_info;
+  void* push_base;
+  int64_t push_rank_stride;
+  int32_t push_entries, push_ranks;
 };
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -567,6 +629,8 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
   kp.rows_per_expert = d->rows_per_expert; kp.Mw = d->Mw; kp.accumulate = d->accumulate;
   kp.zero_empty_below = d->zero_empty_below;
   kp.debug = d->debug;
+  kp.src_info = d->src_info; kp.push_base = d->push_base; kp.push_rank_stride = d->push_rank_stride;
+  kp.push_entries = d->push_entries; kp.push_ranks = d->push_ranks;
   kp.out[0] = d->out[0]; kp.out[1] = d->out[1]; kp.out[2] = d->out[2];
   kp.row_scale = d->row_scale; kp.ldc = d->ldc; kp.status = d->status;
   kp.timeout_ns = (unsigned long long)(d->timeout_ns > 0 ? d->timeout_ns : 2000000000ll);
@@ -619,6 +683,12 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
   if (d->epi == EPI_F32)
     return d->b_mn ? launch_gemm<false, false, true, EPI_F32>(kp, grid, stream)
                    : launch_gemm<false, false, false, EPI_F32>(kp, grid, stream);
+  if (d->epi == EPI_PUSH) {
+    if (d->src_info == nullptr || d->push_base == nullptr || d->push_entries <= 0)
+      return fail(-9, "gemm: the push epilogue needs src_info and a staging buffer");
+    return d->b_mn ? launch_gemm<false, false, true, EPI_PUSH>(kp, grid, stream)
+                   : launch_gemm<false, false, false, EPI_PUSH>(kp, grid, stream);
+  }
   return fail(-7, "gemm: unknown epilogue %d", d->epi);
 }
 

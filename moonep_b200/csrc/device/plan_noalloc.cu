@@ -127,7 +127,7 @@ extern "C" int mep_plan_local_noalloc(const int32_t* tpe_all, const int32_t* top
   p.sync.status = scratch + NOALLOC_TABLE_INTS + 8;       // [8]
   p.sync.timeout_ns = 0; p.sync.kernel_id = KID_PLAN;
   p.E = E; p.epn = E / R; p.S = S; p.K = K; p.token_padding = token_padding;
-  p.N = (int64_t)S * K; p.NvS = NvS; p.tpe_off = 0; p.link_off = 0;
+  p.N = (int64_t)S * K; p.NvS = NvS; p.tpe_off = 0; p.link_off = 0; p.src_off = 0;
   p.topk = topk; p.tpe = nullptr; p.dst = dst; p.cu_seqlens = cu_seqlens; p.zero_fill = zero_fill;
   p.etc = etc; p.remote_stats = remote_stats;
   p.scratch = scratch; p.scratch_ints = NOALLOC_INTS;

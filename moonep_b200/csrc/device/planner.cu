@@ -133,7 +133,9 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) ep_plan_kernel(const PlanPara
       for (int j = K - 1; j > k; --j)
         if (dr[j] == dr[k]) next = (int)(raw[j] - (int64_t)dr[j] * p.NvS);
       int64_t row = raw[k] - (int64_t)dr[k] * p.NvS;
-      sc.meta[(size_t)dr[k] * sc.meta_stride + p.link_off + row] = next | (dup ? LINK_DUP_BIT : 0);
+      int32_t* peer = sc.meta + (size_t)dr[k] * sc.meta_stride;
+      peer[p.link_off + row] = next | (dup ? LINK_DUP_BIT : 0);
+      peer[p.src_off + row] = (int32_t)((int64_t)rank * p.N + (int64_t)t * K + k);
       if (dup) d[k] = -raw[k] - 1;
     }
   }
@@ -161,7 +163,7 @@ int mep_launch_plan(const void* ctx_, const int32_t* topk, const int32_t* tpe, i
   p.sync = c.sync(KID_PLAN);
   p.E = c.E; p.epn = c.epn; p.S = c.S; p.K = c.K; p.token_padding = c.token_padding;
   p.N = c.N; p.NvS = c.NvS;
-  p.tpe_off = c.ml.tpe_off; p.link_off = c.ml.link_off;
+  p.tpe_off = c.ml.tpe_off; p.link_off = c.ml.link_off; p.src_off = c.ml.src_off;
   p.topk = topk; p.tpe = tpe; p.dst = dst; p.cu_seqlens = cu_seqlens; p.zero_fill = zero_fill;
   p.etc = etc; p.remote_stats = remote_stats;
   p.scratch = c.plan_scratch; p.scratch_ints = c.plan_scratch_ints;

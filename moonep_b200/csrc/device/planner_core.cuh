@@ -13,7 +13,7 @@ struct PlanParams {
   SyncCtx sync;
   int E, epn, S, K, token_padding;
   int64_t N, NvS;
-  int64_t tpe_off, link_off;
+  int64_t tpe_off, link_off, src_off;
   const int32_t* topk;      // [Rv][N]
   const int32_t* tpe;       // [Rv][E]
   int32_t* dst;             // [Rv][N]

@@ -12,11 +12,11 @@ extern "C" {
 int64_t mep_meta_chunk_ints(int64_t NvS, int R, int E) { return meta_layout(NvS, R, E).total; }
 int64_t mep_plan_scratch_ints(int R, int E, int num_sms) { return plan_scratch_ints(R, E, num_sms); }
 int mep_sync_state_ints() { return SYNC_STATE_INTS; }
-// out[5]: weights_off, link_off, tpe_off, flags_off, arrive_off
+// out[6]: weights_off, link_off, tpe_off, flags_off, arrive_off, src_off
 void mep_meta_offsets(int64_t NvS, int R, int E, int64_t* out) {
   MetaLayout m = meta_layout(NvS, R, E);
   out[0] = m.weights_off; out[1] = m.link_off; out[2] = m.tpe_off; out[3] = m.flags_off;
-  out[4] = m.arrive_off;
+  out[4] = m.arrive_off; out[5] = m.src_off;
 }
 
 // Returns an opaque handle (0 on failure, see mep_last_error).

@@ -8,8 +8,10 @@ experts followed by this rank's prefetch slots), runs its grouped GEMM over the 
 calls ``reduce_grad``.  This module is that integration:
 
 forward   logits = x Wr -> top-k/softmax/histogram -> ``dispatch`` (fresh plan) ->
-          ``prefetch_weight`` -> gate/up GEMM with fused SwiGLU x route weight -> down GEMM
-          written straight into the Buffer's shard -> ``combine`` (zero copy)
+          ``prefetch_weight`` -> gate/up GEMM with fused SwiGLU x route weight -> down GEMM whose
+          epilogue pushes every result row over NVLink to the token's home rank
+          (``fused_combine``) -> ``combine_pushed`` (barrier + local K-sum); or, unfused, down
+          GEMM into the Buffer's shard -> ``combine`` (zero copy)
 backward  ``dispatch(plan=...)`` of dy -> down dgrad / wgrad -> SwiGLU backward (also yields the
           route-weight grads) -> gate/up wgrad and dgrad (into the shard) -> ``combine`` with the
           weight-gather path (returns d route weights as [S, K]) -> ``reduce_grad`` -> router
@@ -84,9 +86,16 @@ class _MoEFn(torch.autograd.Function):
         act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use,
                                            wg_slot=slots["g"], wu_slot=slots["u"], split=split,
                                            row_scale=w_nvs, save_gate_up=layer.training)
-        shard = buf.hidden_nvsh_buffer_view
-        gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split, out=shard)
-        y, _, _ = buf.combine(plan, shard, None, zero_copy=True)
+        if layer.fused_combine:
+            # down GEMM fused with the combine all-to-all: the epilogue stores every result row
+            # into its entry's slot on the token's home rank while later tiles are still computing
+            gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split,
+                      push=buf.push_target(plan))
+            y, _ = buf.combine_pushed(plan)
+        else:
+            shard = buf.hidden_nvsh_buffer_view
+            gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split, out=shard)
+            y, _, _ = buf.combine(plan, shard, None, zero_copy=True)
         ctx.layer, ctx.plan, ctx.split = layer, plan, split
         ctx.save_for_backward(x, hidden, w_nvs, cu_use, act, gate, up, topk, w)
         layer.last_plan = plan
@@ -111,11 +120,16 @@ class _MoEFn(torch.autograd.Function):
         d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
         gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
         gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
-        shard = buf.hidden_nvsh_buffer_view
-        gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
-                          wu_slot=slot("up"), split=split, out=shard)
-        # dispatch backward = combine; the weight-gather path returns d(route weights) [S, K]
-        dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
+        # dispatch backward = combine; the scalar path returns d(route weights) as [S, K]
+        if layer.fused_combine:
+            gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
+                              wu_slot=slot("up"), split=split, push=buf.push_target(plan))
+            dx, dw_sk = buf.combine_pushed(plan, d_scale)
+        else:
+            shard = buf.hidden_nvsh_buffer_view
+            gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
+                              wu_slot=slot("up"), split=split, out=shard)
+            dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
         if have_slots and pools.reduce:
             buf.reduce_grad(plan, local_gate_grad=layer.g_gate, local_up_grad=layer.g_up,
                             local_down_grad=layer.g_down, gate_reduce_buffer=pools.reduce["gate"],
@@ -134,12 +148,15 @@ class MoELayer:
 
     def __init__(self, buf: Buffer, Hp: int, pools: Optional[ExpertPools] = None, *, seed: int = 0,
                  router_bias: Optional[torch.Tensor] = None, init_std: float = 0.02,
-                 train: bool = True):
+                 train: bool = True, fused_combine: bool = True):
         assert not buf.virtual, "MoELayer runs one rank per process"
         assert buf.token_padding % 64 == 0, "the grouped GEMM needs token_padding % 64 == 0"
         assert buf.H % 128 == 0 and Hp % 64 == 0
         self.buf, self.pools, self.Hp = buf, pools, Hp
         self.training, self.accumulate_grads = train, False
+        self.fused_combine = fused_combine
+        if fused_combine:
+            buf.enable_push()
         dev = torch.device("cuda", buf.device)
         H, E, epn = buf.H, buf.E, buf.epn
         g = torch.Generator(device=dev).manual_seed(seed * 7919 + 13)

@@ -30,7 +30,7 @@ import torch
 from .. import _native as nat
 from .._native import I, P
 
-EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
+EPI_BF16, EPI_SWIGLU, EPI_F32, EPI_PUSH = 0, 1, 2, 3
 
 
 class _GemmDesc(ctypes.Structure):
@@ -45,6 +45,9 @@ class _GemmDesc(ctypes.Structure):
         ("b", (ctypes.c_void_p * 2) * 2), ("b_rows", ctypes.c_int64 * 2), ("ldb", ctypes.c_int64),
         ("cu_seqlens", ctypes.c_void_p), ("out", ctypes.c_void_p * 3), ("ldc", ctypes.c_int64),
         ("row_scale", ctypes.c_void_p), ("status", ctypes.c_void_p), ("timeout_ns", ctypes.c_int64),
+        ("src_info", ctypes.c_void_p), ("push_base", ctypes.c_void_p),
+        ("push_rank_stride", ctypes.c_int64), ("push_entries", ctypes.c_int32),
+        ("push_ranks", ctypes.c_int32),
     ]
 
 
@@ -97,7 +100,7 @@ def _groups(cu_seqlens, rows):
 
 
 def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_expert, b_mn, epi,
-                 outs, ldc, row_scale=None, total_rows=None, grid=0):
+                 outs, ldc, row_scale=None, total_rows=None, grid=0, push=None):
     d = _GemmDesc()
     d.mode, d.epi, d.b_mn, d.nseg = 0, epi, int(b_mn), len(a_segs)
     cu_ptr, ngroups = _groups(cu_seqlens, None)
@@ -135,6 +138,12 @@ def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_ex
     d.ldc = ldc
     d.row_scale = None if row_scale is None else row_scale.data_ptr()
     d.status = status_word(a0.device).data_ptr()
+    if push is not None:
+        d.epi = EPI_PUSH
+        d.src_info = push["src_info"].data_ptr()
+        d.push_base = push["push_base"].data_ptr()
+        d.push_rank_stride = push["push_rank_stride"]
+        d.push_entries, d.push_ranks = push["push_entries"], push["push_ranks"]
     _launch(d)
 
 
@@ -156,11 +165,18 @@ def gateup_swiglu(x, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=No
     return act, gate, up
 
 
-def down(act, wd, cu_seqlens, *, wd_slot=None, split=None, out=None):
-    """``y[rows,H] = act[rows,H'] Wd[g]^T`` with ``wd`` [G0, H, H']."""
+def down(act, wd, cu_seqlens, *, wd_slot=None, split=None, out=None, push=None):
+    """``y[rows,H] = act[rows,H'] Wd[g]^T`` with ``wd`` [G0, H, H'].
+
+    With ``push`` (``Buffer.push_target(plan)``) nothing is written locally: every result row goes
+    over NVLink into its entry's slot on the token's home rank (finish with
+    ``Buffer.combine_pushed``) and ``None`` is returned."""
     rows, Hp = act.shape
     H = wd.shape[1]
     assert wd.shape[2] == Hp
+    if push is not None:
+        _tokens_gemm([act], [wd], [wd_slot], cu_seqlens, split, H, Hp, H, False, EPI_BF16, [], H, push=push)
+        return None
     y = torch.empty(rows, H, dtype=torch.bfloat16, device=act.device) if out is None else out
     _tokens_gemm([act], [wd], [wd_slot], cu_seqlens, split, H, Hp, H, False, EPI_BF16, [y], y.stride(0))
     return y
@@ -175,10 +191,16 @@ def down_dgrad(dy, wd, cu_seqlens, *, wd_slot=None, split=None):
     return out
 
 
-def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None, out=None):
-    """``dx[rows,H] = dg Wg[g]^T + du Wu[g]^T`` (two K segments into one accumulator)."""
+def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None, out=None,
+                 push=None):
+    """``dx[rows,H] = dg Wg[g]^T + du Wu[g]^T`` (two K segments into one accumulator); ``push`` as
+    in :func:`down`."""
     rows, Hp = dg.shape
     H = wg.shape[1]
+    if push is not None:
+        _tokens_gemm([dg, du], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, H, Hp, H, False,
+                     EPI_BF16, [], H, push=push)
+        return None
     dx = torch.empty(rows, H, dtype=torch.bfloat16, device=dg.device) if out is None else out
     _tokens_gemm([dg, du], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, H, Hp, H, False,
                  EPI_BF16, [dx], dx.stride(0))

@@ -30,6 +30,7 @@ class CommPlan:
     E: int
     NvS: int
     K: int
+    src_info: Optional[torch.Tensor] = None   # [NvS] int32: owner entry of every received row
     _dedup_cache: dict = field(default_factory=dict, compare=False, repr=False)
 
     def clone(self) -> "CommPlan":
@@ -41,6 +42,7 @@ class CommPlan:
             remote_stats=self.remote_stats.clone(),
             cu_seqlens=self.cu_seqlens.clone(),
             link=self.link.clone(),
+            src_info=None if self.src_info is None else self.src_info.clone(),
             _dedup_cache={},
         )
 
