@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--maxvio", type=float, default=2.0, help="target routing imbalance")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--small", action="store_true", help="reduced shape for profiling captures (not a bench)")
+    ap.add_argument("--no-fused-combine", action="store_true",
+                    help="down GEMM into the shard + pull combine instead of the push epilogue")
     ap.add_argument("--experts", type=int, default=E,
                     help="total experts; anything but 256 is a profiling shape, not the benchmark")
     return ap.parse_args()
@@ -148,7 +150,7 @@ def run_ours(args):
     s, h, hp, k, e = (512, 1024, 512, 4, 32) if args.small else (S, H, HP, K, args.experts)
     buf = Buffer(s, h, k, e, R, num_sms=NUM_SMS if R > 1 else 16, token_padding=TOKEN_PADDING)
     pools = ExpertPools(R, e // R, h, hp, buf.group, rank) if R > 1 else None
-    layer = MoELayer(buf, hp, pools, seed=0)
+    layer = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     n_batches = 4
     host = [torch.randn(s, h, generator=torch.Generator().manual_seed(1000 * rank + i)).bfloat16().pin_memory()
@@ -265,6 +267,7 @@ def run_ours(args):
                    "tokens_per_rank": s, "token_padding": TOKEN_PADDING, "num_sms_comm": buf.num_sms,
                    "maxvio_target": args.maxvio, "maxvio_achieved": mv,
                    "step": "forward + backward + SGD update, fp32 weight grads",
+                   "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",
                    "l2": "working set per step (>= 8 GB of weights, grads and activations) exceeds the 126 MB L2; no explicit flush"},
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": s * h * 2, "d2h_bytes_per_step": 4,
