@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--maxvio", type=float, default=2.0, help="target routing imbalance")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--small", action="store_true", help="reduced shape for profiling captures (not a bench)")
+    ap.add_argument("--weight-sms", type=int, default=12,
+                    help="CTAs of prefetch_weight / reduce_grad, which run next to the GEMMs")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="down GEMM into the shard + pull combine instead of the push epilogue")
     ap.add_argument("--experts", type=int, default=E,
@@ -148,7 +150,8 @@ def run_ours(args):
     if R > 1:
         dist.init_process_group("nccl", device_id=dev)
     s, h, hp, k, e = (512, 1024, 512, 4, 32) if args.small else (S, H, HP, K, args.experts)
-    buf = Buffer(s, h, k, e, R, num_sms=NUM_SMS if R > 1 else 16, token_padding=TOKEN_PADDING)
+    buf = Buffer(s, h, k, e, R, num_sms=NUM_SMS if R > 1 else 16, token_padding=TOKEN_PADDING,
+                 num_sms_weights=args.weight_sms)
     pools = ExpertPools(R, e // R, h, hp, buf.group, rank) if R > 1 else None
     layer = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
@@ -264,7 +267,7 @@ def run_ours(args):
         "config": {"model": "deepseek-v3-style MoE layer: router 7168->256 top-8 softmax, 256 SwiGLU experts H=7168 H'=2048"
                    if not args.small and args.experts == E else f"profiling shape (experts={e})",
                    "global_batch": tokens, "seq_len": s, "parallelism": f"ep{R}",
-                   "tokens_per_rank": s, "token_padding": TOKEN_PADDING, "num_sms_comm": buf.num_sms,
+                   "tokens_per_rank": s, "token_padding": TOKEN_PADDING, "num_sms_comm": buf.num_sms, "num_sms_weight_ops": buf.num_sms_weights,
                    "maxvio_target": args.maxvio, "maxvio_achieved": mv,
                    "step": "forward + backward + SGD update, fp32 weight grads",
                    "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",

@@ -40,7 +40,7 @@ nat.declare("mep_meta_chunk_ints", L, [L, I, I])
 nat.declare("mep_plan_scratch_ints", L, [I, I, I])
 nat.declare("mep_sync_state_ints", I, [])
 nat.declare("mep_meta_offsets", None, [L, I, I, ctypes.POINTER(ctypes.c_int64)])
-nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
+nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
 nat.declare("mep_ctx_destroy", None, [P])
 nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P])
 nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, P, I, I, P])
@@ -91,7 +91,7 @@ class Buffer:
                  num_sms: Optional[int] = None, token_padding: int = 128, group=None,
                  comm_stream_priority: int = -1, enable_pdl: bool = True,
                  explicitly_destroy: bool = False, *, virtual: bool = False,
-                 timeout_s: Optional[float] = None):
+                 timeout_s: Optional[float] = None, num_sms_weights: Optional[int] = None):
         for name, v in dict(S=S, H=H, K=K, E=E, num_ep_ranks=num_ep_ranks,
                             token_padding=token_padding).items():
             assert isinstance(v, int) and v > 0, f"{name} must be a positive int, got {v!r}"
@@ -127,6 +127,8 @@ class Buffer:
             num_sms = 32 if num_sms is None else num_sms
             assert num_sms <= props.multi_processor_count
         self.num_sms = int(num_sms)
+        # CTAs of prefetch_weight / reduce_grad; a small number lets them run next to a GEMM
+        self.num_sms_weights = int(num_sms_weights) if num_sms_weights else self.num_sms
         self.num_sms_local = _default_num_sms_local(props.multi_processor_count)
         self.Rv = R if self.virtual else 1
         self.NvS = (self.N + (token_padding - 1) * 2 * self.epn + token_padding - 1) \
@@ -163,13 +165,14 @@ class Buffer:
             dist.barrier(group=self.group)
 
         # ---- local state ------------------------------------------------------------------
-        self.sync_state = torch.zeros(self.Rv, nat.call("mep_sync_state_ints"), dtype=torch.int32, device=dev)
+        self.sync_state = torch.zeros(2, self.Rv, nat.call("mep_sync_state_ints"), dtype=torch.int32, device=dev)
         self.status = torch.zeros(8, dtype=torch.int32).pin_memory()
         self.plan_scratch = torch.empty(
             self.Rv, int(nat.call("mep_plan_scratch_ints", R, E, self.num_sms)), dtype=torch.int32, device=dev)
         self._ctx = nat.call(
             "mep_ctx_create", self.rank, R, int(self.virtual), E, S, K, H, token_padding,
-            self.num_sms, self.num_sms_local, self.hidden_buf.data_ptr(), self.hidden_stride,
+            self.num_sms, self.num_sms_local, self.num_sms_weights, self.hidden_buf.data_ptr(),
+            self.hidden_stride,
             self.meta_buf.data_ptr(), self.meta_stride, self.sync_state.data_ptr(),
             self.status.data_ptr(), self.plan_scratch.data_ptr(), int(self.timeout_s * 1e9))
         if not self._ctx:
@@ -240,7 +243,7 @@ class Buffer:
         self.status.zero_()
         self.sync_state.zero_()
         rows = self._meta_rows()
-        rows[:, self.flags_off: self.flags_off + self.R].zero_()
+        rows[:, self.flags_off: self.flags_off + 2 * ((self.R + 31) // 32 * 32)].zero_()
         torch.cuda.synchronize(self.device)
         if not self._solo:
             dist.barrier(group=self.group)

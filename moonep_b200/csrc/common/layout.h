@@ -43,7 +43,9 @@ MEP_HD int64_t nvs_rows(int64_t S, int64_t K, int64_t epn, int64_t token_padding
 //   WEIGHTS  [NvS]        fp32 route weights, slot order (bit-cast)
 //   LINK     [NvS]        duplicate chain links written by the source ranks
 //   TPE      [2][R][E]    gathered tokens-per-expert, double buffered by plan parity
-//   FLAGS    [R]          barrier arrival epochs, slot p is written by rank p
+//   FLAGS    [2][R]       barrier arrival epochs, slot p is written by rank p; channel 0 serves
+//                         dispatch / combine, channel 1 the weight ops (prefetch_weight,
+//                         reduce_grad), so the two families may run concurrently
 //   ARRIVE   [NvS/128+1]  per-128-row tile arrival counters (fused dispatch->GEMM path)
 //   SRC      [NvS]        per slot: source_rank * (S*K) + (token*K + k) of the entry that owns
 //                         it, written by the source ranks' planners (-1 on padding rows); the
@@ -57,7 +59,7 @@ MEP_HD MetaLayout meta_layout(int64_t NvS, int64_t R, int64_t E) {
   m.link_off = align_up64(NvS, 4);
   m.tpe_off = m.link_off + align_up64(NvS, 4);
   m.flags_off = m.tpe_off + align_up64(2 * R * E, 4);
-  m.arrive_off = m.flags_off + align_up64(R, 32);
+  m.arrive_off = m.flags_off + 2 * align_up64(R, 32);
   m.src_off = m.arrive_off + align_up64(NvS / 128 + 1, 32);
   m.total = m.src_off + align_up64(NvS, 4);
   return m;

@@ -218,7 +218,7 @@ static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, cudaStream_t str
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(c.num_sms, c.Rv());
+  dim3 grid(c.num_sms_weights, c.Rv());
   MEP_CUDA_OK(launch_coop((const void*)ep_grad_reduce_kernel<ST>, grid, dim3(GR_THREADS), smem, stream, p));
   return 0;
 }
@@ -244,7 +244,7 @@ int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* co
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (n < 1 || n > GR_MAX_TENSORS) return fail(-1, "reduce_grad: %d tensors (1..%d)", n, GR_MAX_TENSORS);
   GradReduceParams p;
-  p.sync = c.sync(KID_REDUCE);
+  p.sync = c.sync(KID_REDUCE, /*channel=*/1);
   p.epn = c.epn; p.n_tensors = n; p.etc = etc; p.entry_barrier = entry_barrier;
   p.zero_consumed = zero_consumed;
   for (int t = 0; t < n; ++t) {

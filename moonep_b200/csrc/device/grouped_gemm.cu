@@ -54,6 +54,7 @@ struct GemmKParams {
   const int32_t* cu_seqlens;
   int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
   int debug;   // timing experiments only: 1 = skip epilogue stores, 2 = skip TMEM loads
+  int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
   void* out[3];
   const float* row_scale;
   long long ldc;
@@ -111,6 +112,7 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     t.n0 = ni * BN;
     t.num_kb = (t.rows + BK - 1) / BK;
     if (t.rows <= 0 && t.g >= p.zero_empty_below) t.valid = false;
+    if (t.g < p.g_begin) t.valid = false;
   } else {
     // largest g with prefix[g] * n_tiles_n <= id
     int lo = 0, hi = p.ngroups - 1;
@@ -121,7 +123,7 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     t.g = lo;
     int start = t.g == 0 ? 0 : s_end[t.g - 1];
     int len = s_end[t.g] - start;
-    int mt = (len + BM - 1) / BM;
+    int mt = max(1, (len + BM - 1) / BM);
     int local = id - s_prefix[t.g] * n_tiles_n;
     int ni = local / mt, mi = local - ni * mt;
     t.row0 = start + mi * BM;
@@ -171,7 +173,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       int g = g0 + lane;
       int len = 0;
       if (g < p.ngroups) len = s_end[g] - (g == 0 ? 0 : s_end[g - 1]);
-      int mt = len > 0 ? (len + BM - 1) / BM : 0;
+      int mt = (len > 0 && g >= p.g_begin) ? (len + BM - 1) / BM : 0;
       int incl = mt;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -540,7 +542,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 struct GemmDesc {
   int32_t mode, epi, b_mn, nseg;
   int32_t ngroups, split, total_rows, N, K, rows_per_expert, Mw, accumulate, zero_empty_below, grid;
-  int32_t debug, pad_;
+  int32_t debug, g_begin;
   int64_t a_rows;
   int64_t lda[2];
   const void* a[2];
@@ -628,7 +630,7 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
   kp.total_rows = d->total_rows; kp.N = d->N; kp.K = d->K; kp.nseg = d->nseg;
   kp.rows_per_expert = d->rows_per_expert; kp.Mw = d->Mw; kp.accumulate = d->accumulate;
   kp.zero_empty_below = d->zero_empty_below;
-  kp.debug = d->debug;
+  kp.debug = d->debug; kp.g_begin = d->g_begin;
   kp.src_info = d->src_info; kp.push_base = d->push_base; kp.push_rank_stride = d->push_rank_stride;
   kp.push_entries = d->push_entries; kp.push_ranks = d->push_ranks;
   kp.out[0] = d->out[0]; kp.out[1] = d->out[1]; kp.out[2] = d->out[2];

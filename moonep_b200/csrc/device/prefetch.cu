@@ -171,7 +171,7 @@ static int launch_prefetch_t(const BufferCtx& c, PrefetchParams& p, cudaStream_t
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(c.num_sms, c.Rv());
+  dim3 grid(c.num_sms_weights, c.Rv());
   MEP_CUDA_OK(launch_coop((const void*)ep_prefetch_kernel<ST>, grid, dim3(PF_THREADS), smem, stream, p));
   return 0;
 }
@@ -190,7 +190,7 @@ int mep_launch_prefetch(const void* ctx_, const int32_t* etc, int n, const void*
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (n < 1 || n > PF_MAX_TENSORS) return fail(-1, "prefetch: %d tensors (1..%d)", n, PF_MAX_TENSORS);
   PrefetchParams p;
-  p.sync = c.sync(KID_PREFETCH);
+  p.sync = c.sync(KID_PREFETCH, /*channel=*/1);
   p.epn = c.epn; p.n_tensors = n; p.etc = etc;
   for (int t = 0; t < n; ++t) {
     if (expert_bytes[t] % 16 != 0 || rank_stride[t] % 16 != 0 ||

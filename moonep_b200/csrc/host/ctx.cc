@@ -21,7 +21,7 @@ void mep_meta_offsets(int64_t NvS, int R, int E, int64_t* out) {
 
 // Returns an opaque handle (0 on failure, see mep_last_error).
 void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int token_padding,
-                     int num_sms, int num_sms_local, void* hidden, int64_t hidden_stride_rows,
+                     int num_sms, int num_sms_local, int num_sms_weights, void* hidden, int64_t hidden_stride_rows,
                      void* meta, int64_t meta_stride_ints, void* sync_state, void* status,
                      void* plan_scratch, int64_t timeout_ns) {
   if (R <= 0 || E <= 0 || E % R != 0 || S <= 0 || K <= 0 || K > MAX_TOPK || R > MAX_RANKS) {
@@ -31,6 +31,7 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
   BufferCtx* c = new BufferCtx();
   c->rank = rank; c->R = R; c->virt = virt; c->E = E; c->epn = E / R; c->S = S; c->K = K; c->H = H;
   c->token_padding = token_padding; c->num_sms = num_sms; c->num_sms_local = num_sms_local;
+  c->num_sms_weights = num_sms_weights > 0 ? num_sms_weights : num_sms;
   c->N = (int64_t)S * K;
   c->NvS = nvs_rows(S, K, c->epn, token_padding);
   if (c->NvS > MAX_NVS || (int64_t)R * c->NvS > INT32_MAX) {

@@ -17,14 +17,14 @@ namespace mep {
 
 struct BufferCtx {
   int rank, R, virt;
-  int E, epn, S, K, H, token_padding, num_sms, num_sms_local;
+  int E, epn, S, K, H, token_padding, num_sms, num_sms_local, num_sms_weights;
   int64_t N, NvS;
   void* hidden;            // bf16 [R][hidden_stride_rows][H], symmetric
   int64_t hidden_stride;   // rows between consecutive ranks' shards
   int32_t* meta;           // int32 [R][meta_stride], symmetric
   int64_t meta_stride;
   MetaLayout ml;
-  int32_t* sync_state;     // [Rv][SYNC_STATE_INTS]
+  int32_t* sync_state;     // [2 channels][Rv][SYNC_STATE_INTS]
   int32_t* status;         // host-visible [8]
   int32_t* plan_scratch;   // [Rv][plan_scratch_ints]
   int64_t plan_scratch_ints;
@@ -32,14 +32,17 @@ struct BufferCtx {
   int sm_count;
 
   int Rv() const { return virt ? R : 1; }
-  SyncCtx sync(int kernel_id) const {
+  // channel 0: dispatch / combine; channel 1: prefetch_weight / reduce_grad.  Each channel has
+  // its own flag slots, epoch and grid-barrier word, so one kernel of each family may be in
+  // flight at the same time (on different streams) without disturbing the other's barriers.
+  SyncCtx sync(int kernel_id, int channel = 0) const {
     SyncCtx s;
     s.rank_base = virt ? 0 : rank;
     s.R = R;
     s.meta = meta;
     s.meta_stride = meta_stride;
-    s.flags_off = ml.flags_off;
-    s.sync_state = sync_state;
+    s.flags_off = ml.flags_off + (int64_t)channel * align_up64(R, 32);
+    s.sync_state = sync_state + (size_t)channel * Rv() * SYNC_STATE_INTS;
     s.status = status;
     s.timeout_ns = timeout_ns;
     s.kernel_id = kernel_id;

@@ -72,20 +72,27 @@ class _MoEFn(torch.autograd.Function):
         hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
         pools = layer.pools
         if pools is not None and pools.prefetch:
+            # the owners push the redundant experts' weights on the comm stream while this stream
+            # already runs the gate/up GEMM of the local experts (which need no prefetched weight)
+            # on the SMs the copy kernel leaves free; the prefetch slots follow in a second launch
             ev = buf.prefetch_weight(
                 plan, async_finish=True, local_gate_weight=layer.w_gate,
                 local_up_weight=layer.w_up, local_down_weight=layer.w_down,
                 gate_prefetch_buffer=pools.prefetch["gate"], up_prefetch_buffer=pools.prefetch["up"],
                 down_prefetch_buffer=pools.prefetch["down"])
-            torch.cuda.current_stream().wait_event(ev)
             slots = dict(g=pools.slot("gate"), u=pools.slot("up"), d=pools.slot("down"))
+            split, cu_use = epn, cu
+            outs = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu[:epn], row_scale=w_nvs,
+                                      save_gate_up=layer.training, grid=layer.overlap_grid())
+            torch.cuda.current_stream().wait_event(ev)
+            act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu, wg_slot=slots["g"],
+                                               wu_slot=slots["u"], split=epn, row_scale=w_nvs,
+                                               save_gate_up=layer.training, out=outs, g_begin=epn)
         else:
             slots = dict(g=None, u=None, d=None)
-        split = epn if slots["g"] is not None else None
-        cu_use = cu if split is not None else cu[:epn]
-        act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use,
-                                           wg_slot=slots["g"], wu_slot=slots["u"], split=split,
-                                           row_scale=w_nvs, save_gate_up=layer.training)
+            split, cu_use = None, cu[:epn]
+            act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use, row_scale=w_nvs,
+                                               save_gate_up=layer.training)
         if layer.fused_combine:
             # down GEMM fused with the combine all-to-all: the epilogue stores every result row
             # into its entry's slot on the token's home rank while later tiles are still computing
@@ -120,26 +127,32 @@ class _MoEFn(torch.autograd.Function):
         d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
         gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
         gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
+        # the replicas' weight grads travel home on the comm stream while this stream computes dX
+        ev_r = None
+        if have_slots and pools.reduce:
+            ev_r = buf.reduce_grad(plan, async_finish=True, local_gate_grad=layer.g_gate,
+                                   local_up_grad=layer.g_up, local_down_grad=layer.g_down,
+                                   gate_reduce_buffer=pools.reduce["gate"], up_reduce_buffer=pools.reduce["up"],
+                                   down_reduce_buffer=pools.reduce["down"],
+                                   zero_consumed=layer.accumulate_grads)   # overwritten next step otherwise
+        grid = layer.overlap_grid() if ev_r is not None else 0
         # dispatch backward = combine; the scalar path returns d(route weights) as [S, K]
         if layer.fused_combine:
             gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
-                              wu_slot=slot("up"), split=split, push=buf.push_target(plan))
+                              wu_slot=slot("up"), split=split, push=buf.push_target(plan), grid=grid)
             dx, dw_sk = buf.combine_pushed(plan, d_scale)
         else:
             shard = buf.hidden_nvsh_buffer_view
             gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
-                              wu_slot=slot("up"), split=split, out=shard)
+                              wu_slot=slot("up"), split=split, out=shard, grid=grid)
             dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
-        if have_slots and pools.reduce:
-            buf.reduce_grad(plan, local_gate_grad=layer.g_gate, local_up_grad=layer.g_up,
-                            local_down_grad=layer.g_down, gate_reduce_buffer=pools.reduce["gate"],
-                            up_reduce_buffer=pools.reduce["up"], down_reduce_buffer=pools.reduce["down"],
-                            zero_consumed=layer.accumulate_grads)   # overwritten next step otherwise
         # router backward
         d_logits = ew.router_topk_bwd(w, dw_sk, topk, buf.E)                 # [S, E] bf16
         gemm.wgrad(x, d_logits, None, layer.g_router, accumulate=acc)
         dx_r = gemm.dense(d_logits, layer.w_router, b_is_kn=False, out_dtype=torch.bfloat16)
         dx = dx + dx_r
+        if ev_r is not None:
+            torch.cuda.current_stream().wait_event(ev_r)      # grads are complete for the optimizer
         return dx, None
 
 
@@ -172,6 +185,11 @@ class MoELayer:
             self.g_router = z(1, H, E)
             self.g_gate, self.g_up, self.g_down = z(epn, H, Hp), z(epn, H, Hp), z(epn, H, Hp)
         self.last_plan = None
+
+    def overlap_grid(self) -> int:
+        """CTAs a GEMM may use while a weight op (prefetch / reduce) runs next to it."""
+        sms = torch.cuda.get_device_properties(self.buf.device).multi_processor_count
+        return max(1, sms - self.buf.num_sms_weights)
 
     def parameters(self):
         return dict(router=self.w_router, gate=self.w_gate, up=self.w_up, down=self.w_down)

@@ -40,7 +40,7 @@ class _GemmDesc(ctypes.Structure):
         ("total_rows", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
         ("rows_per_expert", ctypes.c_int32), ("Mw", ctypes.c_int32),
         ("accumulate", ctypes.c_int32), ("zero_empty_below", ctypes.c_int32),
-        ("grid", ctypes.c_int32), ("debug", ctypes.c_int32), ("pad_", ctypes.c_int32),
+        ("grid", ctypes.c_int32), ("debug", ctypes.c_int32), ("g_begin", ctypes.c_int32),
         ("a_rows", ctypes.c_int64), ("lda", ctypes.c_int64 * 2), ("a", ctypes.c_void_p * 2),
         ("b", (ctypes.c_void_p * 2) * 2), ("b_rows", ctypes.c_int64 * 2), ("ldb", ctypes.c_int64),
         ("cu_seqlens", ctypes.c_void_p), ("out", ctypes.c_void_p * 3), ("ldc", ctypes.c_int64),
@@ -100,7 +100,7 @@ def _groups(cu_seqlens, rows):
 
 
 def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_expert, b_mn, epi,
-                 outs, ldc, row_scale=None, total_rows=None, grid=0, push=None):
+                 outs, ldc, row_scale=None, total_rows=None, grid=0, push=None, g_begin=0):
     d = _GemmDesc()
     d.mode, d.epi, d.b_mn, d.nseg = 0, epi, int(b_mn), len(a_segs)
     cu_ptr, ngroups = _groups(cu_seqlens, None)
@@ -110,6 +110,7 @@ def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_ex
     d.total_rows = a0.shape[0] if total_rows is None else total_rows
     d.N, d.K, d.rows_per_expert, d.Mw = N, K, rows_per_expert, 0
     d.grid = grid
+    d.g_begin = g_begin
     d.a_rows = a0.shape[0]
     for i, a in enumerate(a_segs):
         _bf16(a, "A")
@@ -148,20 +149,26 @@ def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_ex
 
 
 def gateup_swiglu(x, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None,
-                  row_scale=None, save_gate_up=True):
+                  row_scale=None, save_gate_up=True, out=None, g_begin=0, grid=0):
     """``act[rows,H'] = silu(x Wg[g]) * (x Wu[g]) * row_scale``; also returns bf16 gate / up.
 
-    ``x`` [rows, H]; ``wg``/``wu`` [G0, H, H'] (+ optional slot tensors for groups >= split)."""
+    ``x`` [rows, H]; ``wg``/``wu`` [G0, H, H'] (+ optional slot tensors for groups >= split).
+    ``out=(act, gate, up)`` reuses existing outputs and ``g_begin`` skips the first groups, so the
+    local experts and the prefetch slots can be computed by two launches; ``grid`` limits the
+    number of CTAs (to leave SMs to a concurrent communication kernel)."""
     rows, H = x.shape
     Hp = wg.shape[2]
     assert wg.shape[1] == H and wu.shape == wg.shape
-    act = torch.empty(rows, Hp, dtype=torch.bfloat16, device=x.device)
-    gate = torch.empty_like(act) if save_gate_up else None
-    up = torch.empty_like(act) if save_gate_up else None
+    if out is not None:
+        act, gate, up = out
+    else:
+        act = torch.empty(rows, Hp, dtype=torch.bfloat16, device=x.device)
+        gate = torch.empty_like(act) if save_gate_up else None
+        up = torch.empty_like(act) if save_gate_up else None
     if row_scale is not None:
         assert row_scale.dtype == torch.float32 and row_scale.numel() >= rows
     _tokens_gemm([x], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, Hp, H, H, True, EPI_SWIGLU,
-                 [gate, up, act], Hp, row_scale)
+                 [gate, up, act], Hp, row_scale, grid=grid, g_begin=g_begin)
     return act, gate, up
 
 
@@ -192,18 +199,18 @@ def down_dgrad(dy, wd, cu_seqlens, *, wd_slot=None, split=None):
 
 
 def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None, out=None,
-                 push=None):
+                 push=None, grid=0):
     """``dx[rows,H] = dg Wg[g]^T + du Wu[g]^T`` (two K segments into one accumulator); ``push`` as
     in :func:`down`."""
     rows, Hp = dg.shape
     H = wg.shape[1]
     if push is not None:
         _tokens_gemm([dg, du], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, H, Hp, H, False,
-                     EPI_BF16, [], H, push=push)
+                     EPI_BF16, [], H, push=push, grid=grid)
         return None
     dx = torch.empty(rows, H, dtype=torch.bfloat16, device=dg.device) if out is None else out
     _tokens_gemm([dg, du], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, H, Hp, H, False,
-                 EPI_BF16, [dx], dx.stride(0))
+                 EPI_BF16, [dx], dx.stride(0), grid=grid)
     return dx
 
 

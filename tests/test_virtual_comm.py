@@ -160,7 +160,7 @@ def test_barrier_many_rounds_and_sync_kernel():
     for _ in range(2000):
         buf.inter_rank_sync()
     buf.check()
-    assert buf.sync_state[:, 1].tolist() == [2000] * 8
+    assert buf.sync_state[0, :, 1].tolist() == [2000] * 8
 
 
 def test_bounded_wait_reports_status_and_recovers():
@@ -173,7 +173,7 @@ def test_bounded_wait_reports_status_and_recovers():
     buf = Buffer(8, 64, 2, 4, 2, num_sms=1, token_padding=8, virtual=True, timeout_s=0.2)
     buf.inter_rank_sync()
     buf.check()
-    buf.sync_state[0, 1] += 5            # rank 0 now waits for an epoch rank 1 never reaches
+    buf.sync_state[0, 0, 1] += 5            # rank 0 now waits for an epoch rank 1 never reaches
     torch.cuda.synchronize()
     buf.inter_rank_sync()
     with pytest.raises(CommTimeoutError) as exc:
