@@ -39,7 +39,8 @@ def parse():
     ap.add_argument("--maxvio", type=float, default=2.0, help="target routing imbalance")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--small", action="store_true", help="reduced shape for profiling captures (not a bench)")
-    ap.add_argument("--weight-sms", type=int, default=12,
+    ap.add_argument("--trace", action="store_true", help="also print a per-span device-time table")
+    ap.add_argument("--weight-sms", type=int, default=16,
                     help="CTAs of prefetch_weight / reduce_grad, which run next to the GEMMs")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="down GEMM into the shard + pull combine instead of the push epilogue")
@@ -282,6 +283,17 @@ def run_ours(args):
         "remote_stats": stats.get("remote_stats"), "dedup_ratio": stats.get("dedup_ratio"),
         "clocks": clocks,
     }
+    if args.trace:
+        from moonep_b200.utils.trace import Tracer
+        layer.tracer = Tracer(enabled=True)
+        for i in range(5):
+            step(xs[i % n_batches])
+        spans = layer.tracer.summary()
+        names = list(spans)
+        t = torch.tensor([spans[n]["mean_ms"] for n in names], device=dev)
+        if R > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["trace_ms_max_over_ranks"] = {n: round(float(v), 3) for n, v in zip(names, t)}
     if rank == 0:
         print(json.dumps(out), flush=True)
     buf.destroy()

@@ -30,6 +30,7 @@ from .. import buffer as symm
 from ..api import Buffer
 from ..ops import elementwise as ew
 from ..ops import gemm
+from ..utils.trace import NULL_TRACER
 
 
 class ExpertPools:
@@ -67,9 +68,12 @@ class _MoEFn(torch.autograd.Function):
     def forward(ctx, x, layer):
         buf: Buffer = layer.buf
         epn = buf.epn
-        logits = gemm.dense(x, layer.w_router)                         # [S, E] fp32
-        topk, w, tpe = ew.router_topk(logits, buf.K, layer.router_bias)
-        hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
+        tr = layer.tracer
+        with tr.span("f.router"):
+            logits = gemm.dense(x, layer.w_router)                         # [S, E] fp32
+            topk, w, tpe = ew.router_topk(logits, buf.K, layer.router_bias)
+        with tr.span("f.dispatch"):
+            hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
         pools = layer.pools
         if pools is not None and pools.prefetch:
             # the owners push the redundant experts' weights on the comm stream while this stream
@@ -82,12 +86,15 @@ class _MoEFn(torch.autograd.Function):
                 down_prefetch_buffer=pools.prefetch["down"])
             slots = dict(g=pools.slot("gate"), u=pools.slot("up"), d=pools.slot("down"))
             split, cu_use = epn, cu
-            outs = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu[:epn], row_scale=w_nvs,
-                                      save_gate_up=layer.training, grid=layer.overlap_grid())
-            torch.cuda.current_stream().wait_event(ev)
-            act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu, wg_slot=slots["g"],
-                                               wu_slot=slots["u"], split=epn, row_scale=w_nvs,
-                                               save_gate_up=layer.training, out=outs, g_begin=epn)
+            with tr.span("f.gateup_local"):
+                outs = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu[:epn], row_scale=w_nvs,
+                                          save_gate_up=layer.training, grid=layer.overlap_grid())
+            with tr.span("f.wait_prefetch"):
+                torch.cuda.current_stream().wait_event(ev)
+            with tr.span("f.gateup_slots"):
+                act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu, wg_slot=slots["g"],
+                                                   wu_slot=slots["u"], split=epn, row_scale=w_nvs,
+                                                   save_gate_up=layer.training, out=outs, g_begin=epn)
         else:
             slots = dict(g=None, u=None, d=None)
             split, cu_use = None, cu[:epn]
@@ -96,9 +103,11 @@ class _MoEFn(torch.autograd.Function):
         if layer.fused_combine:
             # down GEMM fused with the combine all-to-all: the epilogue stores every result row
             # into its entry's slot on the token's home rank while later tiles are still computing
-            gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split,
-                      push=buf.push_target(plan))
-            y, _ = buf.combine_pushed(plan)
+            with tr.span("f.down_push"):
+                gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split,
+                          push=buf.push_target(plan))
+            with tr.span("f.combine_pushed"):
+                y, _ = buf.combine_pushed(plan)
         else:
             shard = buf.hidden_nvsh_buffer_view
             gemm.down(act, layer.w_down, cu_use, wd_slot=slots["d"], split=split, out=shard)
@@ -120,13 +129,19 @@ class _MoEFn(torch.autograd.Function):
         dy = dy.contiguous()
         # combine backward = dispatch with the saved plan; the view is consumed before the shard
         # is overwritten further down (same stream)
-        d_out, _, _, _ = buf.dispatch(dy, plan=plan, zero_copy=True)
-        d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split)
+        tr = layer.tracer
+        with tr.span("b.dispatch"):
+            d_out, _, _, _ = buf.dispatch(dy, plan=plan, zero_copy=True)
+        with tr.span("b.down_dgrad"):
+            d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split)
         acc = layer.accumulate_grads
-        gemm.wgrad(d_out, act, cu, layer.g_down, grad_slot=gslot("down"), split=split, accumulate=acc)
-        d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
-        gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
-        gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
+        with tr.span("b.wgrad_down"):
+            gemm.wgrad(d_out, act, cu, layer.g_down, grad_slot=gslot("down"), split=split, accumulate=acc)
+        with tr.span("b.swiglu_bwd"):
+            d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
+        with tr.span("b.wgrad_gateup"):
+            gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
+            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
         # the replicas' weight grads travel home on the comm stream while this stream computes dX
         ev_r = None
         if have_slots and pools.reduce:
@@ -138,21 +153,25 @@ class _MoEFn(torch.autograd.Function):
         grid = layer.overlap_grid() if ev_r is not None else 0
         # dispatch backward = combine; the scalar path returns d(route weights) as [S, K]
         if layer.fused_combine:
-            gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
-                              wu_slot=slot("up"), split=split, push=buf.push_target(plan), grid=grid)
-            dx, dw_sk = buf.combine_pushed(plan, d_scale)
+            with tr.span("b.gateup_dgrad_push"):
+                gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
+                                  wu_slot=slot("up"), split=split, push=buf.push_target(plan), grid=grid)
+            with tr.span("b.combine_pushed"):
+                dx, dw_sk = buf.combine_pushed(plan, d_scale)
         else:
             shard = buf.hidden_nvsh_buffer_view
             gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
                               wu_slot=slot("up"), split=split, out=shard, grid=grid)
             dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
         # router backward
-        d_logits = ew.router_topk_bwd(w, dw_sk, topk, buf.E)                 # [S, E] bf16
-        gemm.wgrad(x, d_logits, None, layer.g_router, accumulate=acc)
-        dx_r = gemm.dense(d_logits, layer.w_router, b_is_kn=False, out_dtype=torch.bfloat16)
-        dx = dx + dx_r
+        with tr.span("b.router"):
+            d_logits = ew.router_topk_bwd(w, dw_sk, topk, buf.E)                 # [S, E] bf16
+            gemm.wgrad(x, d_logits, None, layer.g_router, accumulate=acc)
+            dx_r = gemm.dense(d_logits, layer.w_router, b_is_kn=False, out_dtype=torch.bfloat16)
+            dx = dx + dx_r
         if ev_r is not None:
-            torch.cuda.current_stream().wait_event(ev_r)      # grads are complete for the optimizer
+            with tr.span("b.wait_reduce_grad"):
+                torch.cuda.current_stream().wait_event(ev_r)      # grads are complete for the optimizer
         return dx, None
 
 
@@ -168,6 +187,7 @@ class MoELayer:
         self.buf, self.pools, self.Hp = buf, pools, Hp
         self.training, self.accumulate_grads = train, False
         self.fused_combine = fused_combine
+        self.tracer = NULL_TRACER
         if fused_combine:
             buf.enable_push()
         dev = torch.device("cuda", buf.device)
@@ -204,10 +224,11 @@ class MoELayer:
     def sgd_step(self, lr: float) -> None:
         """``w -= lr * grad`` on every parameter (the router grad is averaged over the group by
         the caller if it wants data-parallel semantics; experts are rank-private)."""
-        ew.sgd_update_(self.w_router, self.g_router[0], lr)
-        ew.sgd_update_(self.w_gate, self.g_gate, lr)
-        ew.sgd_update_(self.w_up, self.g_up, lr)
-        ew.sgd_update_(self.w_down, self.g_down, lr)
+        with self.tracer.span("sgd"):
+            ew.sgd_update_(self.w_router, self.g_router[0], lr)
+            ew.sgd_update_(self.w_gate, self.g_gate, lr)
+            ew.sgd_update_(self.w_up, self.g_up, lr)
+            ew.sgd_update_(self.w_down, self.g_down, lr)
 
     def state_dict(self):
         """Home-layout weights only; prefetch slots are transient and never saved."""
