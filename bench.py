@@ -39,6 +39,7 @@ def parse():
     ap.add_argument("--maxvio", type=float, default=2.0, help="target routing imbalance")
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--small", action="store_true", help="reduced shape for profiling captures (not a bench)")
+    ap.add_argument("--no-graph", action="store_true", help="issue the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--trace", action="store_true", help="also print a per-span device-time table")
     ap.add_argument("--weight-sms", type=int, default=16,
                     help="CTAs of prefetch_weight / reduce_grad, which run next to the GEMMs")
@@ -195,13 +196,33 @@ def run_ours(args):
     for i in range(max(args.warmup, 3)):
         step(xs[i % n_batches])
     buf.check()
+    # The whole step (forward + backward + SGD, ~300 launches) is captured into one CUDA graph;
+    # the timed loops replay it.  Falls back to eager issue if capture is not possible.
+    eager_step, graphed = step, False
+    nat.LAUNCHES = 0
+    eager_step(xs[0])
+    launches_per_step = nat.LAUNCHES          # kernels of this library launched by one step
+    if not args.no_graph:
+        try:
+            from moonep_b200.utils.graph import GraphedStep
+            gs = GraphedStep(lambda x: eager_step(x), [xs[0]], warmup=1)
+            step = lambda x: gs(x)
+            graphed = True
+            for i in range(2):
+                step(xs[i % n_batches])
+            buf.check()
+        except Exception as exc:  # noqa: BLE001
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed, running eagerly: {type(exc).__name__}: {exc}",
+                      file=sys.stderr, flush=True)
+            step = eager_step
+            torch.cuda.synchronize()
     # ---- device-timed: inputs resident on the device ------------------------------------------
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    nat.LAUNCHES = 0
     ms_step = timed(lambda i: step(xs[i % n_batches]), args.steps)
-    launches = nat.LAUNCHES
+    launches = launches_per_step * args.steps   # replayed from the graph when graphed
     # ---- end to end: pinned host batch -> device every step, loss read back every step ---------
     # A two-deep input pipeline, as a data loader would run it: while step i computes, the copy
     # stream uploads batch i+1 from pinned memory.  Every step still performs its own H2D copy
@@ -272,6 +293,7 @@ def run_ours(args):
                    "maxvio_target": args.maxvio, "maxvio_achieved": mv,
                    "step": "forward + backward + SGD update, fp32 weight grads",
                    "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",
+                   "cuda_graph": graphed,
                    "l2": "working set per step (>= 8 GB of weights, grads and activations) exceeds the 126 MB L2; no explicit flush"},
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": s * h * 2, "d2h_bytes_per_step": 4,
@@ -287,13 +309,16 @@ def run_ours(args):
         from moonep_b200.utils.trace import Tracer
         layer.tracer = Tracer(enabled=True)
         for i in range(5):
-            step(xs[i % n_batches])
+            eager_step(xs[i % n_batches])
         spans = layer.tracer.summary()
         names = list(spans)
         t = torch.tensor([spans[n]["mean_ms"] for n in names], device=dev)
+        tmin = t.clone()
         if R > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
         out["trace_ms_max_over_ranks"] = {n: round(float(v), 3) for n, v in zip(names, t)}
+        out["trace_ms_min_over_ranks"] = {n: round(float(v), 3) for n, v in zip(names, tmin)}
     if rank == 0:
         print(json.dumps(out), flush=True)
     buf.destroy()

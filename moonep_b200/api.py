@@ -268,8 +268,10 @@ class Buffer:
     def _run_async(self, tensors, fn):
         """Run ``fn`` on the comm stream after the current stream's work; return its event."""
         main = torch.cuda.current_stream()
+        capturing = torch.cuda.is_current_stream_capturing()
         for t in tensors:
-            if isinstance(t, torch.Tensor) and t.is_cuda:
+            # under graph capture the tensors live in the graph's private pool for its lifetime
+            if isinstance(t, torch.Tensor) and t.is_cuda and not capturing:
                 t.record_stream(self.comm_stream)
         self.comm_stream.wait_event(main.record_event())
         with torch.cuda.stream(self.comm_stream):
@@ -318,7 +320,7 @@ class Buffer:
         if async_finish:
             out, ev = self._run_async([hidden_sh, route_weights_sk, topk_experts_sk, tokens_per_expert], run)
             for t in out[:3]:
-                if isinstance(t, torch.Tensor):
+                if isinstance(t, torch.Tensor) and not torch.cuda.is_current_stream_capturing():
                     t.record_stream(torch.cuda.current_stream())
             return (*out, ev)
         return run()
@@ -392,7 +394,7 @@ class Buffer:
         if async_finish:
             (h, w), ev = self._run_async([hidden_nvsh, route_weights_nvs], run)
             for t in (h, w):
-                if isinstance(t, torch.Tensor):
+                if isinstance(t, torch.Tensor) and not torch.cuda.is_current_stream_capturing():
                     t.record_stream(torch.cuda.current_stream())
             return h, w, ev
         h, w = run()
