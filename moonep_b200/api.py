@@ -583,9 +583,10 @@ class Buffer:
         return out
 
     # ---- teardown ---------------------------------------------------------------------------------
-    def destroy(self) -> None:
+    def destroy(self, group_barrier: bool = True) -> None:
         """Idempotent.  Synchronises, meets the group, then unmaps the symmetric buffers
-        (views first, owners last) -- moonep/api.py:512-553."""
+        (views first, owners last) -- moonep/api.py:512-553.  ``group_barrier=False`` skips the
+        collective meeting: the way out when a peer is known to be gone."""
         if self._destroyed:
             return
         self._destroyed = True
@@ -594,7 +595,7 @@ class Buffer:
         try:
             self.comm_stream.synchronize()
             torch.cuda.synchronize(self.device)
-            if not self._solo and dist.is_initialized():
+            if group_barrier and not self._solo and dist.is_initialized():
                 dist.barrier(group=self.group)
         finally:
             nat.call("mep_ctx_destroy", self._ctx)

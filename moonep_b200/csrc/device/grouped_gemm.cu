@@ -44,6 +44,10 @@ constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int MAX_GROUPS = 1024;
 constexpr int GEMM_SMEM = GEMM_STAGES * STAGE_BYTES + 1024;
+// CTA-pair variant: each CTA stages A (16 KB) and half of B (16 KB) per k-block, six stages.
+constexpr int GEMM_STAGES2 = 6;
+constexpr int STAGE_BYTES2 = A_TILE_BYTES + B_TILE_BYTES / 2;
+constexpr int GEMM_SMEM2 = GEMM_STAGES2 * STAGE_BYTES2 + 1024;
 
 enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2, EPI_PUSH = 3 };
 
@@ -51,6 +55,7 @@ struct GemmKParams {
   CUtensorMap a[2];
   CUtensorMap b[2][2];
   CUtensorMap c[2];        // weight-grad output (fp32), per allocation
+  CUtensorMap b2[2][2];    // K-major B with a 128-row box (CTA-pair variant)
   const int32_t* cu_seqlens;
   int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
   int debug;   // timing experiments only: 1 = skip epilogue stores, 2 = skip TMEM loads
@@ -74,10 +79,10 @@ struct Tile {
 
 __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volatile int* s_abort,
                                           const GemmKParams& p, int where) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait_cluster(bar, parity)) return true;
   unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_cluster(bar, parity)) {
     if ((++spins & 255u) == 0) {
       if (*s_abort) return false;
       if (globaltimer_ns() - t0 > p.timeout_ns) {
@@ -94,9 +99,11 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
-template <bool WGRAD, int EPI>
+// TWO: the tile list counts PAIRS of 128-row tiles (256 rows of one group); CTA `crank` of the
+// pair takes the rows [256*mi + 128*crank, +128) and may end up with none in a group's last pair.
+template <bool WGRAD, int EPI, bool TWO = false>
 __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int* s_end,
-                                         const int* s_prefix, int n_tiles_n) {
+                                         const int* s_prefix, int n_tiles_n, int crank = 0) {
   Tile t;
   t.valid = true;
   if constexpr (WGRAD) {
@@ -123,11 +130,12 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     t.g = lo;
     int start = t.g == 0 ? 0 : s_end[t.g - 1];
     int len = s_end[t.g] - start;
-    int mt = max(1, (len + BM - 1) / BM);
+    constexpr int TM = TWO ? 2 * BM : BM;
+    int mt = max(1, (len + TM - 1) / TM);
     int local = id - s_prefix[t.g] * n_tiles_n;
     int ni = local / mt, mi = local - ni * mt;
-    t.row0 = start + mi * BM;
-    t.rows = min(BM, s_end[t.g] - t.row0);
+    t.row0 = start + mi * TM + crank * BM;
+    t.rows = max(0, min(BM, s_end[t.g] - t.row0));
     t.m0 = 0;
     t.n0 = ni * (EPI == EPI_SWIGLU ? BN / 2 : BN);
     t.num_kb = p.nseg * ((p.K + BK - 1) / BK);
@@ -137,14 +145,21 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
   return t;
 }
 
-template <bool WGRAD, bool A_MN, bool B_MN, int EPI>
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
+  static_assert(!(TWO && WGRAD), "the CTA-pair variant covers the token-major modes");
+  constexpr int GEMM_STAGES = TWO ? GEMM_STAGES2 : mep::GEMM_STAGES;
+  constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
+  const int crank = TWO ? (int)cluster_cta_rank() : 0;        // 0 = leader of the pair
+  const int work_id0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int work_stride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t full[GEMM_STAGES];
   __shared__ __align__(8) uint64_t empty[GEMM_STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ __align__(8) uint64_t peer_full[TWO ? GEMM_STAGES2 : 1];   // leader: peer's stage landed
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_end[MAX_GROUPS];
@@ -158,7 +173,9 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
+    if constexpr (TWO)
+      for (int s = 0; s < GEMM_STAGES; ++s) mbar_init(&peer_full[s], 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -173,7 +190,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       int g = g0 + lane;
       int len = 0;
       if (g < p.ngroups) len = s_end[g] - (g == 0 ? 0 : s_end[g - 1]);
-      int mt = (len > 0 && g >= p.g_begin) ? (len + BM - 1) / BM : 0;
+      constexpr int TM = TWO ? 2 * BM : BM;
+      int mt = (len > 0 && g >= p.g_begin) ? (len + TM - 1) / TM : 0;
       int incl = mt;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -186,11 +204,12 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     if (lane == 0) s_prefix[p.ngroups] = run;
   }
   if (warp == 1) {
-    tmem_alloc(&s_tmem, 512);
-    tmem_relinquish();
+    if constexpr (TWO) { tmem_alloc2(&s_tmem, 512); tmem_relinquish2(); }
+    else { tmem_alloc(&s_tmem, 512); tmem_relinquish(); }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (TWO) cluster_sync_all();     // the peer's barriers exist before anyone arrives on them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem;
 
@@ -207,8 +226,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       tma_prefetch_desc(&p.b[0][0]);
       int it = 0;
       bool ok = true;
-      for (long long id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+      for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
+        Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
         if (!t.valid) continue;
         const int kb_per_seg = WGRAD ? t.num_kb : (p.K + BK - 1) / BK;
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
@@ -234,7 +253,20 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           } else {
             tma_load_2d(sa, &p.a[seg], k0, t.row0, &full[s]);
             const int erow = t.g_local * p.rows_per_expert;
-            if constexpr (B_MN) {
+            if constexpr (TWO) {
+              // this CTA's half of the B tile: N columns [128*crank, +128) of the pair's tile
+              if constexpr (B_MN) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                  if constexpr (EPI == EPI_SWIGLU)   // leader: 128 gate columns, peer: 128 up columns
+                    tma_load_2d(sb + j * 8192, &p.b[crank][t.alloc], t.n0 + 64 * j, erow + k0, &full[s]);
+                  else
+                    tma_load_2d(sb + j * 8192, &p.b[seg][t.alloc], t.n0 + 128 * crank + 64 * j, erow + k0, &full[s]);
+                }
+              } else {
+                tma_load_2d(sb, &p.b2[seg][t.alloc], k0, erow + t.n0 + 128 * crank, &full[s]);
+              }
+            } else if constexpr (B_MN) {
 #pragma unroll
               for (int j = 0; j < BN / 64; ++j) {
                 if constexpr (EPI == EPI_SWIGLU) {
@@ -254,12 +286,25 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_instr_desc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && TWO && crank != 0) {
+      // peer CTA of a pair: no MMA to issue; tell the leader when each of MY stages has landed
+      int it = 0;
+      bool ok = true;
+      for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
+        Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
+        if (!t.valid) continue;
+        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+          const int s = it % GEMM_STAGES;
+          if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 5)) { ok = false; break; }
+          mbar_arrive_remote(&peer_full[s], 0);
+        }
+      }
+    } else if (lane == 0) {
+      constexpr uint32_t idesc = make_instr_desc_bf16(TWO ? 2 * BM : BM, BN, A_MN, B_MN);
       int it = 0, tile_n = 0;
       bool ok = true;
-      for (long long id = blockIdx.x; id < total_tiles && ok; id += gridDim.x) {
-        Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+      for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
+        Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
         if (!t.valid) continue;
         const int acc = tile_n & 1;
         if (tile_n >= 2 &&
@@ -269,6 +314,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % GEMM_STAGES;
           if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 3)) { ok = false; break; }
+          if constexpr (TWO)
+            if (!gemm_wait(&peer_full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 6)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_TILE_BYTES;
@@ -278,12 +325,16 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
                                      : make_smem_desc(sb + kk * 32, 16, 1024);
-            umma_bf16(tacc, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            if constexpr (TWO) umma_bf16_2cta(tacc, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            else umma_bf16(tacc, da, db, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
-          umma_commit(&empty[s]);       // stage reusable once these MMAs have read it
+          // stage reusable (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (TWO) umma_commit_2cta(&empty[s], 3);
+          else umma_commit(&empty[s]);
         }
         if (!ok) break;
-        umma_commit(&acc_full[acc]);    // accumulator complete
+        if constexpr (TWO) umma_commit_2cta(&acc_full[acc], 3);   // accumulator complete, both halves
+        else umma_commit(&acc_full[acc]);
         ++tile_n;
       }
     }
@@ -292,8 +343,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     const int q = warp & 3;
     const int r_in_tile = q * 32 + lane;
     int tile_n = 0;
-    for (long long id = blockIdx.x; id < total_tiles; id += gridDim.x) {
-      Tile t = get_tile<WGRAD, EPI>(p, (int)id, s_end, s_prefix, n_tiles_n);
+    for (long long id = work_id0; id < total_tiles; id += work_stride) {
+      Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
       if (!t.valid) continue;
       const int acc = tile_n & 1;
       if (!gemm_wait(&acc_full[acc], (uint32_t)(tile_n >> 1) & 1u, abortp, p, 4)) break;
@@ -520,7 +571,10 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if (TWO && crank != 0) mbar_arrive_remote(&acc_empty[acc], 0);   // the leader issues the MMAs
+        else mbar_arrive(&acc_empty[acc]);
+      }
       ++tile_n;
     }
   }
@@ -532,9 +586,11 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     while (globaltimer_ns() - t0 < 200000ull) { }
   }
   if (warp >= 2 && lane == 0) bulk_wait<0>();   // epilogue TMA stores have completed
+  if constexpr (TWO) cluster_sync_all();        // neither CTA leaves while its peer may still touch it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (TWO) tmem_dealloc2(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -559,6 +615,7 @@ struct GemmDesc {
   void* push_base;
   int64_t push_rank_stride;
   int32_t push_entries, push_ranks;
+  int32_t two_cta, pad2_;
 };
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -598,6 +655,30 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-12, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+// CTA-pair launch: clusters of two CTAs, one pair per two SMs.
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
+  auto kern = ep_grouped_gemm_kernel<false, A_MN, B_MN, EPI, true>;
+  static bool configured = false;
+  if (!configured) {
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM2));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)(grid / 2 * 2));
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = GEMM_SMEM2;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  MEP_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, kp));
   return 0;
 }
 
@@ -671,23 +752,32 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       const int64_t rows = d->b[s < nsel ? s : 0][al] ? d->b_rows[al] : d->b_rows[0];
       if (d->b_mn) {   // [K rows][N cols] per expert
         if ((rc = make_map(&kp.b[s][al], base, rows, d->N, d->ldb, 64, BK))) return rc;
+        kp.b2[s][al] = kp.b[s][al];
       } else {         // [N rows][K cols] per expert
         if ((rc = make_map(&kp.b[s][al], base, rows, d->K, d->ldb, BK, BN))) return rc;
+        if ((rc = make_map(&kp.b2[s][al], base, rows, d->K, d->ldb, BK, BN / 2))) return rc;
       }
     }
+  const bool two = d->two_cta != 0 && grid >= 2;
   if (d->epi == EPI_SWIGLU) {
     if (!d->b_mn) return fail(-6, "swiglu epilogue expects MN-major weights");
+    if (two) return launch_gemm2<false, true, EPI_SWIGLU>(kp, grid, stream);
     return launch_gemm<false, false, true, EPI_SWIGLU>(kp, grid, stream);
   }
-  if (d->epi == EPI_BF16)
+  if (d->epi == EPI_BF16) {
+    if (two) return d->b_mn ? launch_gemm2<false, true, EPI_BF16>(kp, grid, stream)
+                            : launch_gemm2<false, false, EPI_BF16>(kp, grid, stream);
     return d->b_mn ? launch_gemm<false, false, true, EPI_BF16>(kp, grid, stream)
                    : launch_gemm<false, false, false, EPI_BF16>(kp, grid, stream);
+  }
   if (d->epi == EPI_F32)
     return d->b_mn ? launch_gemm<false, false, true, EPI_F32>(kp, grid, stream)
                    : launch_gemm<false, false, false, EPI_F32>(kp, grid, stream);
   if (d->epi == EPI_PUSH) {
     if (d->src_info == nullptr || d->push_base == nullptr || d->push_entries <= 0)
       return fail(-9, "gemm: the push epilogue needs src_info and a staging buffer");
+    if (two) return d->b_mn ? launch_gemm2<false, true, EPI_PUSH>(kp, grid, stream)
+                            : launch_gemm2<false, false, EPI_PUSH>(kp, grid, stream);
     return d->b_mn ? launch_gemm<false, false, true, EPI_PUSH>(kp, grid, stream)
                    : launch_gemm<false, false, false, EPI_PUSH>(kp, grid, stream);
   }

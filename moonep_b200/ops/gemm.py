@@ -47,7 +47,7 @@ class _GemmDesc(ctypes.Structure):
         ("row_scale", ctypes.c_void_p), ("status", ctypes.c_void_p), ("timeout_ns", ctypes.c_int64),
         ("src_info", ctypes.c_void_p), ("push_base", ctypes.c_void_p),
         ("push_rank_stride", ctypes.c_int64), ("push_entries", ctypes.c_int32),
-        ("push_ranks", ctypes.c_int32),
+        ("push_ranks", ctypes.c_int32), ("two_cta", ctypes.c_int32), ("pad2_", ctypes.c_int32),
     ]
 
 
@@ -73,11 +73,15 @@ def check_status(device="cuda") -> None:
 
 
 DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
+# CTA pairs (tcgen05 cta_group::2, clusters of two CTAs sharing each B tile) for the token-major
+# GEMMs.  ``MOONEP_B200_TWO_CTA=0`` selects the single-CTA kernel.
+TWO_CTA = int(__import__("os").environ.get("MOONEP_B200_TWO_CTA", "1"))
 
 
 def _launch(d: _GemmDesc) -> None:
     global _checked_layout
     d.debug = DEBUG_MODE
+    d.two_cta = TWO_CTA
     if not _checked_layout:
         assert nat.call("mep_gemm_desc_bytes") == ctypes.sizeof(_GemmDesc), "GemmDesc layout mismatch"
         _checked_layout = True

@@ -203,6 +203,40 @@ def decoder_check(R, rank):
         print(f"decoder R={R}: {out}", flush=True)
 
 
+def leave_check(R, rank):
+    """A rank leaves BETWEEN steps (no kernel or collective of its own in flight).  The others
+    learn of it on the host, through the heartbeat, before their next launch: they raise
+    PeerLostError instead of entering a device barrier that would have to time out, and release
+    their Buffer without a group barrier."""
+    from moonep_b200.utils.health import Heartbeat, PeerLostError
+    S, H, K, tp = 64, 128, 2, 16
+    E = 2 * R
+    buf = Buffer(S, H, K, E, R, num_sms=2, token_padding=tp, timeout_s=5.0)
+    hb = Heartbeat.from_default_group()
+    g = torch.Generator(device="cuda").manual_seed(rank)
+    x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    topk = torch.stack([torch.randperm(E, device="cuda", generator=g)[:K] for _ in range(S)]).to(torch.int32)
+    tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+    for step in range(2):
+        hb.step(step, timeout_s=20.0)
+        h, _, _, plan = buf.dispatch(x, None, topk, tpe)
+        out, _, _ = buf.combine(plan, h)
+        buf.check()
+    torch.cuda.synchronize()
+    dist.barrier()
+    if rank == R - 1:
+        os._exit(0)                                  # gone, with nothing in flight
+    try:
+        hb.step(2, timeout_s=2.0)
+        ok = False
+    except PeerLostError as exc:
+        ok = exc.missing == [R - 1]
+    buf.destroy(group_barrier=False)
+    if rank == 0:
+        print(f"MULTIGPU_OK R={R} leave detected={ok}", flush=True)
+    os._exit(0 if ok else 1)
+
+
 def _all_gather(t, R):
     lst = [torch.empty_like(t) for _ in range(R)]
     dist.all_gather(lst, t.contiguous())
@@ -221,6 +255,8 @@ def main():
         layer_check(R, rank)
     if what in ("all", "decoder"):
         decoder_check(R, rank)
+    if what == "leave":
+        leave_check(R, rank)
     dist.barrier()
     if rank == 0:
         print(f"MULTIGPU_OK R={R} {what}", flush=True)
