@@ -159,7 +159,6 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ __align__(8) uint64_t empty[GEMM_STAGES];
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
-  __shared__ __align__(8) uint64_t peer_full[TWO ? GEMM_STAGES2 : 1];   // leader: peer's stage landed
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_end[MAX_GROUPS];
@@ -172,10 +171,9 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   volatile int* abortp = &s_abort;
 
   if (tid == 0) {
-    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    // CTA pairs: both CTAs' loads are credited to the LEADER's full barrier (two producers)
+    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], TWO ? 2 : 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
-    if constexpr (TWO)
-      for (int s = 0; s < GEMM_STAGES; ++s) mbar_init(&peer_full[s], 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -239,7 +237,13 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           }
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
-          mbar_expect_tx(&full[s], STAGE_BYTES);
+          uint32_t lead_bar = 0;
+          if constexpr (TWO) {
+            lead_bar = mapa_u32(&full[s], 0);
+            mbar_expect_tx_cluster(lead_bar, STAGE_BYTES);
+          } else {
+            mbar_expect_tx(&full[s], STAGE_BYTES);
+          }
           const int seg = kb / kb_per_seg;
           const int k0 = (kb - seg * kb_per_seg) * BK;
           if constexpr (WGRAD) {
@@ -251,7 +255,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(sb + j * 8192, &p.b[0][0], t.n0 + 64 * j, t.row0 + k0, &full[s]);
           } else {
-            tma_load_2d(sa, &p.a[seg], k0, t.row0, &full[s]);
+            if constexpr (TWO) tma_load_2d_pair(sa, &p.a[seg], k0, t.row0, lead_bar);
+            else tma_load_2d(sa, &p.a[seg], k0, t.row0, &full[s]);
             const int erow = t.g_local * p.rows_per_expert;
             if constexpr (TWO) {
               // this CTA's half of the B tile: N columns [128*crank, +128) of the pair's tile
@@ -259,12 +264,12 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                   if constexpr (EPI == EPI_SWIGLU)   // leader: 128 gate columns, peer: 128 up columns
-                    tma_load_2d(sb + j * 8192, &p.b[crank][t.alloc], t.n0 + 64 * j, erow + k0, &full[s]);
+                    tma_load_2d_pair(sb + j * 8192, &p.b[crank][t.alloc], t.n0 + 64 * j, erow + k0, lead_bar);
                   else
-                    tma_load_2d(sb + j * 8192, &p.b[seg][t.alloc], t.n0 + 128 * crank + 64 * j, erow + k0, &full[s]);
+                    tma_load_2d_pair(sb + j * 8192, &p.b[seg][t.alloc], t.n0 + 128 * crank + 64 * j, erow + k0, lead_bar);
                 }
               } else {
-                tma_load_2d(sb, &p.b2[seg][t.alloc], k0, erow + t.n0 + 128 * crank, &full[s]);
+                tma_load_2d_pair(sb, &p.b2[seg][t.alloc], k0, erow + t.n0 + 128 * crank, lead_bar);
               }
             } else if constexpr (B_MN) {
 #pragma unroll
@@ -287,18 +292,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   } else if (warp == 1) {
     // ================= MMA issuer =================
     if (lane == 0 && TWO && crank != 0) {
-      // peer CTA of a pair: no MMA to issue; tell the leader when each of MY stages has landed
-      int it = 0;
-      bool ok = true;
-      for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
-        Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
-        if (!t.valid) continue;
-        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-          const int s = it % GEMM_STAGES;
-          if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 5)) { ok = false; break; }
-          mbar_arrive_remote(&peer_full[s], 0);
-        }
-      }
+      // peer CTA of a pair: the leader issues the MMAs for both
     } else if (lane == 0) {
       constexpr uint32_t idesc = make_instr_desc_bf16(TWO ? 2 * BM : BM, BN, A_MN, B_MN);
       int it = 0, tile_n = 0;
@@ -314,8 +308,6 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % GEMM_STAGES;
           if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 3)) { ok = false; break; }
-          if constexpr (TWO)
-            if (!gemm_wait(&peer_full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 6)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_TILE_BYTES;

@@ -87,6 +87,28 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* local_bar, uint32_t
       ::"r"(smem_u32(local_bar)), "r"(cta_rank)
       : "memory");
 }
+// Shared-memory address of the same variable in CTA `cta_rank` of this cluster.
+__device__ __forceinline__ uint32_t mapa_u32(const void* local_ptr, uint32_t cta_rank) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(smem_u32(local_ptr)), "r"(cta_rank));
+  return ra;
+}
+// arrive + expect_tx on a barrier given by its cluster address (possibly in the peer CTA)
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar_cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;"
+               ::"r"(bar_cluster_addr), "r"(bytes)
+               : "memory");
+}
+// Tiled TMA load of a CTA pair: the data lands in THIS CTA's shared memory, the byte count is
+// credited to a barrier that may live in the pair's other CTA (the leader's).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
 // try_wait with cluster-scope acquire, for barriers that receive remote arrivals.
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;

@@ -74,8 +74,10 @@ def check_status(device="cuda") -> None:
 
 DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
 # CTA pairs (tcgen05 cta_group::2, clusters of two CTAs sharing each B tile) for the token-major
-# GEMMs.  ``MOONEP_B200_TWO_CTA=0`` selects the single-CTA kernel.
-TWO_CTA = int(__import__("os").environ.get("MOONEP_B200_TWO_CTA", "1"))
+# GEMMs: ``MOONEP_B200_TWO_CTA=1``.  The variant is numerically verified but its barrier round
+# trip across the pair currently leaves the tensor pipe idle half of the time (0.69 vs
+# 1.29 PFLOP/s), so the single-CTA kernel stays the default.
+TWO_CTA = int(__import__("os").environ.get("MOONEP_B200_TWO_CTA", "0"))
 
 
 def _launch(d: _GemmDesc) -> None:

@@ -117,3 +117,28 @@ def test_dense_router_logits():
     _close(c, a.float() @ b.float(), tol=5e-3)
     c2 = gemm.dense(a, b.t().contiguous(), b_is_kn=False, out_dtype=torch.bfloat16)
     _close(c2, a.float() @ b.float())
+
+
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_cta_pair_variant_matches(b_mn, monkeypatch):
+    """The cta_group::2 kernel (clusters of two CTAs, each staging half of the B tile) gives the
+    same results as the single-CTA kernel, including the SwiGLU epilogue."""
+    from moonep_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(7)
+    groups = [256, 128, 0, 384, 100]
+    ends, rows = _mk(groups)
+    G, H, Hp = len(groups), 256, 384
+    w = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.06).bfloat16()
+    w2 = (torch.randn(G, H, Hp, device="cuda", generator=g) * 0.06).bfloat16()
+    if b_mn:
+        x = torch.randn(rows, H, device="cuda", generator=g).bfloat16()
+        run = lambda: gemm.gateup_swiglu(x, w, w2, ends)
+    else:
+        x = torch.randn(rows, Hp, device="cuda", generator=g).bfloat16()
+        run = lambda: (gemm.down(x, w, ends),)
+    monkeypatch.setattr(gemm, "TWO_CTA", 0)
+    one = [t.clone() for t in run()]
+    monkeypatch.setattr(gemm, "TWO_CTA", 1)
+    two = run()
+    for a, b in zip(one, two):
+        assert torch.equal(a, b)
