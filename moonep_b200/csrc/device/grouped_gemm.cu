@@ -670,6 +670,18 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // A persistent grid must not exceed what is resident at once: not every SM can be paired
+  // into a cluster (GPCs with an odd SM count leave one out), and a second wave of persistent
+  // CTAs would double the run time.
+  static int max_clusters = -1;
+  if (max_clusters < 0) {
+    int n = 0;
+    cudaLaunchConfig_t probe = cfg;
+    probe.gridDim = dim3(2 * 148);
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &probe) != cudaSuccess || n < 1) { cudaGetLastError(); n = 1 << 20; }
+    max_clusters = n;
+  }
+  if ((int)cfg.gridDim.x / 2 > max_clusters) cfg.gridDim = dim3((unsigned)(2 * max_clusters));
   MEP_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, kp));
   return 0;
 }
