@@ -27,6 +27,27 @@ def _unavailable(why: str):
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
+    if int(os.environ.get("WORLD_SIZE", "1")) == 1 and os.environ.get("MOONEP_REF_CHILD") != "1":
+        # One GPU: the reference's native layer ends the process with exit() on a driver error
+        # (csrc/nvl_shared_buffer.cuh:17-39) and it asserts NVLS multicast support even for a
+        # single rank, so it runs in a child process whose failure becomes the `unavailable` line.
+        import subprocess
+        env = dict(os.environ, MOONEP_REF_CHILD="1")
+        cmd = [sys.executable, os.path.join(os.path.dirname(HERE), "bench.py"), "--impl", "reference",
+               "--gpus", "1", "--steps", str(args.steps), "--warmup", str(args.warmup),
+               "--maxvio", str(args.maxvio), "--lr", str(args.lr)]
+        try:
+            res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500)
+        except subprocess.TimeoutExpired:
+            _unavailable("reference run at 1 GPU did not finish within 1500 s")
+            return
+        lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+        if res.returncode == 0 and lines:
+            print(lines[-1], flush=True)
+        else:
+            tail = (res.stderr or res.stdout).strip().splitlines()[-1:] or ["no output"]
+            _unavailable(f"reference process exited with code {res.returncode} at 1 GPU: {tail[0]}")
+        return
     try:
         _run(args)
     except Exception as exc:  # noqa: BLE001 - any failure of the reference is reported, not raised
