@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--maxvio", type=float, default=4.0)
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--impls", default="fused,nccl")
+    ap.add_argument("--no-graph", action="store_true", help="do not capture the fused step in a CUDA graph")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -83,12 +84,28 @@ def main():
         losses = []
         for i in range(args.warmup):
             losses.append(float(model.train_step(*batches[i % 4], args.lr)))
+        # The fused path has static shapes and no host synchronisation, so the whole step
+        # (~2400 launches for 8 layers) replays from one CUDA graph.  The NCCL baseline cannot:
+        # its all_to_all split sizes are read back to the host every layer.
+        run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr)), False
+        if impl == "fused" and not args.no_graph:
+            try:
+                from moonep_b200.utils.graph import GraphedStep
+                gs = GraphedStep(lambda tok, tgt: model.train_step(tok, tgt, args.lr), list(batches[0]), warmup=1)
+                run_step, graphed = (lambda tok, tgt: gs(tok, tgt)), True
+                float(run_step(*batches[1]))
+            except Exception as exc:  # noqa: BLE001
+                if rank == 0:
+                    print(f"[bench_decoder] graph capture failed, eager: {type(exc).__name__}: {exc}",
+                          file=sys.stderr, flush=True)
+                run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr)), False
+                torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
         a, b2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(args.steps):
-            loss = model.train_step(*batches[i % 4], args.lr)
+            loss = run_step(*batches[i % 4])
         b2.record()
         torch.cuda.synchronize()
         ms = torch.tensor([a.elapsed_time(b2) / args.steps], device=dev)
@@ -100,7 +117,7 @@ def main():
         gemm.check_status(dev)
         results[impl] = {"ms_per_step": round(float(ms), 3), "tokens_per_s": round(R * S / float(ms) * 1e3, 1),
                          "peak_mem_gb_max_rank": round(float(peak), 2), "loss_first": losses[0],
-                         "loss_last": float(loss), "maxvio_layer0": round(best[1], 3)}
+                         "loss_last": float(loss), "maxvio_layer0": round(best[1], 3), "cuda_graph": graphed}
         del model
         if buf is not None:
             buf.destroy()
