@@ -37,7 +37,9 @@ def main():
     ap.add_argument("--maxvio", type=float, default=4.0)
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--impls", default="fused,nccl")
-    ap.add_argument("--no-graph", action="store_true", help="do not capture the fused step in a CUDA graph")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the fused step in a CUDA graph (off by default: with the dense-grad NCCL "
+                         "all-reduce inside the graph, process-group teardown has been seen to stall)")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -88,7 +90,7 @@ def main():
         # (~2400 launches for 8 layers) replays from one CUDA graph.  The NCCL baseline cannot:
         # its all_to_all split sizes are read back to the host every layer.
         run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr)), False
-        if impl == "fused" and not args.no_graph:
+        if impl == "fused" and args.graph:
             try:
                 from moonep_b200.utils.graph import GraphedStep
                 gs = GraphedStep(lambda tok, tgt: model.train_step(tok, tgt, args.lr), list(batches[0]), warmup=1)
@@ -129,6 +131,9 @@ def main():
         if "fused" in results and "nccl" in results:
             out["speedup_vs_nccl"] = round(results["nccl"]["ms_per_step"] / results["fused"]["ms_per_step"], 3)
         print(json.dumps(out), flush=True)
+    sys.stdout.flush()
+    if args.graph:
+        os._exit(0)          # see --graph: skip the collective teardown
     dist.destroy_process_group()
 
 
