@@ -1,8 +1,10 @@
 """moonep_b200: a Blackwell-native (sm_100a) expert-parallel communication framework."""
 from .plan import CommPlan  # noqa: F401
 
+MoonEPCommPlan = CommPlan      # the reference's name for the same object (moonep/planning.py:31)
+
 __version__ = "0.1.0"
-__all__ = ["Buffer", "CommPlan", "CommTimeoutError"]
+__all__ = ["Buffer", "CommPlan", "MoonEPCommPlan", "CommTimeoutError"]
 
 
 def __getattr__(name):

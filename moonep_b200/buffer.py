@@ -67,6 +67,25 @@ def _check(rc: int, what: str) -> None:
         raise SymmetricMemoryError(f"{what}: {nat.last_error()} (code {rc})")
 
 
+def nvl_fabric_supported(device: Optional[int] = None) -> bool:
+    """Fabric (multi-node NVLink) memory handles are usable on this device."""
+    device = torch.cuda.current_device() if device is None else device
+    return bool(nat.call("mep_fabric_supported", device))
+
+
+def nvl_multicast_supported(device: Optional[int] = None) -> bool:
+    """The device and driver can create NVSwitch multicast objects."""
+    device = torch.cuda.current_device() if device is None else device
+    return bool(nat.call("mep_multicast_supported", device))
+
+
+def get_multicast_granularity(num_devices: int, nbytes: int) -> int:
+    g = nat.call("mep_multicast_granularity", num_devices, nbytes)
+    if g <= 0:
+        raise SymmetricMemoryError(f"multicast granularity query failed: {nat.last_error()}")
+    return int(g)
+
+
 def get_vmm_granularity(device: Optional[int] = None, fabric: bool = False) -> int:
     device = torch.cuda.current_device() if device is None else device
     g = nat.call("mep_vmm_granularity", device, int(fabric))
