@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--num-sms", type=int, default=32)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-zero", action="store_true", help="reduce_grad without clearing the consumed slots")
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -85,7 +86,7 @@ def main():
     rg = lambda: buf.reduce_grad(
         plan, local_gate_grad=gl["gate"], local_up_grad=gl["up"], local_down_grad=gl["down"],
         gate_reduce_buffer=pools.reduce["gate"], up_reduce_buffer=pools.reduce["up"],
-        down_reduce_buffer=pools.reduce["down"])
+        down_reduce_buffer=pools.reduce["down"], zero_consumed=not a.no_zero)
     us_pf = timed(pf)
     us_rg = timed(rg, prep=fill_reduce)
     buf.check()
@@ -98,7 +99,7 @@ def main():
                "slots_of_busiest_owner": busiest,
                "prefetch_us_worst_rank": round(us_pf, 1), "prefetch_bytes_busiest_owner": push_bytes,
                "prefetch_gbs": round(push_bytes / us_pf / 1e3, 1) if us_pf > 0 else None,
-               "reduce_grad_us_worst_rank": round(us_rg, 1), "reduce_bytes_busiest_owner": pull_bytes,
+               "reduce_grad_us_worst_rank": round(us_rg, 1), "reduce_clears_slots": not a.no_zero, "reduce_bytes_busiest_owner": pull_bytes,
                "reduce_gbs": round(pull_bytes / us_rg / 1e3, 1) if us_rg > 0 else None,
                "nvlink_measured_gbs": NVLINK_MEASURED_GBS, "nvlink_nominal_gbs": NVLINK_NOMINAL_GBS}
         if out["prefetch_gbs"]:

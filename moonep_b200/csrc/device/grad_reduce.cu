@@ -181,30 +181,16 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
   // every home rank has read what it needs before anyone clears
   cross_rank_barrier(sc, 2);
   if (!p.zero_consumed) return;
-  // clear my consumed slots: bulk stores of a zeroed ring stage, many in flight per CTA
-  for (uint32_t i = tid * 16u; i < GR_CHUNK; i += GR_THREADS * 16u)
-    *reinterpret_cast<uint4*>(ring + i) = make_uint4(0, 0, 0, 0);
-  fence_proxy_async_smem();
-  __syncthreads();
-  if (tid == 0) {
-    int pending = 0;
-    int64_t seq = 0;
-    for (int b = 0; b < epn; ++b) {
-      if (etc[rank * epn + b] < 0) continue;
-      for (int t = 0; t < p.n_tensors; ++t) {
-        uint8_t* z = reinterpret_cast<uint8_t*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
-                                                (size_t)b * p.expert_elems[t]);
-        const int64_t bytes = p.expert_elems[t] * 4;
-        for (int64_t off = 0; off < bytes; off += GR_CHUNK, ++seq) {
-          if (seq % G != c) continue;
-          const int64_t rem = bytes - off;
-          bulk_s2g(z + off, ring, (uint32_t)(rem < (int64_t)GR_CHUNK ? rem : (int64_t)GR_CHUNK));
-          if (++pending == 32) { bulk_commit(); bulk_wait_read<2>(); pending = 0; }
-        }
-      }
+  // clear my consumed slots (local memory): 16-byte stores from every thread of the grid
+  for (int b = 0; b < epn; ++b) {
+    if (etc[rank * epn + b] < 0) continue;
+    for (int t = 0; t < p.n_tensors; ++t) {
+      float4* z = reinterpret_cast<float4*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
+                                            (size_t)b * p.expert_elems[t]);
+      const int64_t nv = p.expert_elems[t] / 4;
+      for (int64_t v = (int64_t)c * GR_THREADS + tid; v < nv; v += (int64_t)G * GR_THREADS)
+        z[v] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    bulk_commit();
-    bulk_wait<0>();
   }
 }
 
