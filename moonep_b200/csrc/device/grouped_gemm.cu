@@ -24,6 +24,15 @@
 //        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output.
 // Group g < split reads/writes allocation 0 (local experts), g >= split allocation 1 (this
 // rank's prefetch / reduce slots): the [2*epn] compute view never has to be contiguous.
+// CTA pairs (template TWO, clusters of two CTAs, tcgen05 cta_group::2): the leader issues
+// 256x256x16 MMAs over both CTAs' shared memory; each CTA stages its own 128 rows of A and half
+// of the B tile (32 KB per k-block instead of 48 KB, six stages), which lifts the single-CTA
+// kernel's limit of 12 KB of operand reads per MMA.  Both CTAs' loads count on the LEADER's full
+// barrier, on which only the leader's producer arrives (expecting the bytes of both): a per-stage
+// arrival from the peer over the cluster network measured 2x slower overall.  Token-major pairs
+// cover 256 rows of one group; weight-grad pairs 256 rows of the weight matrix.
+// Measured A/B (32 groups x 1024 rows, H=7168, H'=2048, interleaved runs under the power cap):
+// pairs +13% gate/up, +13% down, +18% down dgrad, +7% gate/up dgrad, +24% weight grad.
 // Every mbarrier wait is bounded; on expiry the CTA records an error, drains and frees TMEM.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -56,10 +65,15 @@ struct GemmKParams {
   CUtensorMap b[2][2];
   CUtensorMap c[2];        // weight-grad output (fp32), per allocation
   CUtensorMap b2[2][2];    // K-major B with a 128-row box (CTA-pair variant)
+  CUtensorMap o;           // bf16 output of the token-major epilogue (32 x 64 store boxes)
   const int32_t* cu_seqlens;
   int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
-  int debug;   // timing experiments only: 1 = skip epilogue stores, 2 = skip TMEM loads
+  // timing experiments only (results are wrong when non-zero), a bit mask: 1 = skip the epilogue's
+  // global stores, 2 = skip its TMEM loads, 4 = issue no MMAs (barriers only), 8 = issue no TMA
+  // loads (barriers only), 16 = plain-store epilogues (results stay correct)
+  int debug;
   int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
+  int tma_out; // outputs are 16-byte aligned: whole 32-row blocks leave through TMA stores
   void* out[3];
   const float* row_scale;
   long long ldc;
@@ -77,12 +91,16 @@ struct Tile {
   bool valid;
 };
 
+// CLUSTER: the barrier also receives plain arrivals from the pair's other CTA, so the wait
+// acquires at cluster scope.  Barriers completed by TMA byte counts or tcgen05.commit do not need it.
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volatile int* s_abort,
                                           const GemmKParams& p, int where) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
+  auto ready = [&] { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  if (ready()) return true;
   unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
+  while (!ready()) {
     if ((++spins & 255u) == 0) {
       if (*s_abort) return false;
       if (globaltimer_ns() - t0 > p.timeout_ns) {
@@ -107,7 +125,8 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
   Tile t;
   t.valid = true;
   if constexpr (WGRAD) {
-    const int mt = p.Mw / BM;
+    constexpr int TMW = TWO ? 2 * BM : BM;       // a pair owns 256 rows of the weight matrix
+    const int mt = p.Mw / TMW;
     const int tpg = mt * n_tiles_n;
     t.g = id / tpg;
     int local = id - t.g * tpg;
@@ -115,7 +134,7 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     int start = t.g == 0 ? 0 : s_end[t.g - 1];
     t.row0 = start;
     t.rows = s_end[t.g] - start;
-    t.m0 = mi * BM;
+    t.m0 = mi * TMW + crank * BM;
     t.n0 = ni * BN;
     t.num_kb = (t.rows + BK - 1) / BK;
     if (t.rows <= 0 && t.g >= p.zero_empty_below) t.valid = false;
@@ -148,7 +167,6 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
 template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
-  static_assert(!(TWO && WGRAD), "the CTA-pair variant covers the token-major modes");
   constexpr int GEMM_STAGES = TWO ? GEMM_STAGES2 : mep::GEMM_STAGES;
   constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
   const int crank = TWO ? (int)cluster_cta_rank() : 0;        // 0 = leader of the pair
@@ -165,14 +183,17 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ int s_prefix[MAX_GROUPS + 1];
   __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];   // per-warp staging pad
   __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
+  // staging of the bf16 epilogue: per warp one 32 x 64 block (128-byte rows, 128B swizzle)
+  __shared__ __align__(1024) uint8_t s_out[(!WGRAD && EPI == EPI_BF16) ? 4 * 4096 : 16];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
   volatile int* abortp = &s_abort;
 
   if (tid == 0) {
-    // CTA pairs: both CTAs' loads are credited to the LEADER's full barrier (two producers)
-    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], TWO ? 2 : 1); mbar_init(&empty[s], 1); }
+    // CTA pairs: both CTAs' loads are credited to the LEADER's full barrier, which only the
+    // leader's producer arrives on (expecting the bytes of both CTAs); no per-stage remote arrive
+    for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
     mbar_fence_init();
     s_abort = 0;
@@ -214,7 +235,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   const int bn_eff = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
   const int n_tiles_n = (p.N + bn_eff - 1) / bn_eff;
   long long total_tiles;
-  if constexpr (WGRAD) total_tiles = (long long)p.ngroups * (p.Mw / BM) * n_tiles_n;
+  if constexpr (WGRAD) total_tiles = (long long)p.ngroups * (p.Mw / (TWO ? 2 * BM : BM)) * n_tiles_n;
   else total_tiles = (long long)s_prefix[p.ngroups] * n_tiles_n;
 
   if (warp == 0) {
@@ -238,15 +259,24 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           uint8_t* sa = tiles + (size_t)s * STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
           uint32_t lead_bar = 0;
-          if constexpr (TWO) {
-            lead_bar = mapa_u32(&full[s], 0);
-            mbar_expect_tx_cluster(lead_bar, STAGE_BYTES);
-          } else {
-            mbar_expect_tx(&full[s], STAGE_BYTES);
+          if constexpr (TWO) lead_bar = mapa_u32(&full[s], 0);
+          if (p.debug & 8) {
+            if (crank == 0) mbar_arrive(&full[s]);
+            continue;
           }
+          // the peer's bytes may land before this arrival: the pending count keeps the phase open
+          if (crank == 0) mbar_expect_tx(&full[s], TWO ? 2 * STAGE_BYTES : STAGE_BYTES);
           const int seg = kb / kb_per_seg;
           const int k0 = (kb - seg * kb_per_seg) * BK;
-          if constexpr (WGRAD) {
+          if constexpr (WGRAD && TWO) {
+            // this CTA's 128 columns of A (t.m0 is already its half) and its half of the B tile
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sa + j * 8192, &p.a[0], t.m0 + 64 * j, t.row0 + k0, lead_bar);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_2d_pair(sb + j * 8192, &p.b[0][0], t.n0 + 128 * crank + 64 * j, t.row0 + k0, lead_bar);
+          } else if constexpr (WGRAD) {
             // A: [token rows][Mw cols], two 64-column blocks; B: [token rows][N cols], four
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
@@ -302,7 +332,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         if (!t.valid) continue;
         const int acc = tile_n & 1;
         if (tile_n >= 2 &&
-            !gemm_wait(&acc_empty[acc], ((uint32_t)(tile_n >> 1) & 1u) ^ 1u, abortp, p, 2)) break;
+            !gemm_wait<TWO>(&acc_empty[acc], ((uint32_t)(tile_n >> 1) & 1u) ^ 1u, abortp, p, 2)) break;
         tc_fence_after();
         const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
@@ -313,6 +343,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           const uint32_t sb = sa + A_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
+            if (p.debug & 4) break;
             const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
@@ -353,9 +384,14 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t rg[32], ru[32];
-          tmem_ld_32x32(tacc + c * 32, rg);
-          tmem_ld_32x32(tacc + 128 + c * 32, ru);
-          tmem_ld_wait();
+          if (!(p.debug & 2)) {
+            tmem_ld_32x32(tacc + c * 32, rg);
+            tmem_ld_32x32(tacc + 128 + c * 32, ru);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) rg[i] = ru[i] = 0u;
+          }
           const int col = t.n0 + c * 32;
           if (row_ok && col < p.N) {
             uint32_t pg[16], pu[16], pa[16];
@@ -376,7 +412,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               pa[i] = *reinterpret_cast<uint32_t*>(&ha);
             }
             const long long off = row * p.ldc + col;
-            if (col + 32 <= p.N) {
+            if (p.debug & 1) {
+            } else if (col + 32 <= p.N) {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 if (og) reinterpret_cast<uint4*>(og + off)[v] = make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
@@ -469,7 +506,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
-            if (have_acc && p.debug != 2) {
+            if (have_acc && !(p.debug & 2)) {
               tmem_ld_32x32(tacc + c * 32, r);
               tmem_ld_wait();
             } else {
@@ -485,7 +522,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             fence_proxy_async_smem();
             __syncwarp();
             const int x0 = col_base + c * 32;
-            if (lane == 0 && x0 < p.N && p.debug != 1) {
+            if (lane == 0 && x0 < p.N && !(p.debug & 1)) {
               if (p.accumulate) tma_reduce_add_2d(cmap, x0, y0, pad);
               else tma_store_2d(cmap, x0, y0, pad);
               bulk_commit();
@@ -503,7 +540,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
-            if (have_acc && p.debug != 2) {
+            if (have_acc && !(p.debug & 2)) {
               tmem_ld_32x32(tacc + c * 32, r);
               tmem_ld_wait();
             } else {
@@ -514,7 +551,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) pad[lane * 33 + i] = __uint_as_float(r[i]);
             __syncwarp();
-            if (col < p.N && p.debug != 1) {
+            if (col < p.N && !(p.debug & 1)) {
               float* o = (float*)outp + off_warp + col;
 #pragma unroll 8
               for (int rr = 0; rr < 32; ++rr) {
@@ -527,11 +564,50 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             }
             __syncwarp();
           }
+        } else if (EPI == EPI_BF16 && !WGRAD && p.tma_out != 0 && q * 32 + 32 <= t.rows) {
+          // all 32 rows of this warp belong to the group: stage 32 x 64 blocks (128-byte rows,
+          // 128B swizzle, conflict-free 16-byte stores) and let the TMA engine write full lines
+          uint8_t* pad = s_out + q * 4096;
+          const int y0 = t.row0 + q * 32;
+#pragma unroll 1
+          for (int c2 = 0; c2 < BN / 64; ++c2) {
+            const int col = col_base + c2 * 64;
+            if (col >= p.N) break;
+            uint32_t ra[32], rb[32];
+            if (have_acc && !(p.debug & 2)) {
+              tmem_ld_32x32(tacc + c2 * 64, ra);
+              tmem_ld_32x32(tacc + c2 * 64 + 32, rb);
+              tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ra[i] = rb[i] = 0u;
+            }
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t* src = j < 4 ? ra + 8 * j : rb + 8 * (j - 4);
+              uint32_t pk[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1]));
+                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(pad + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                  make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && !(p.debug & 1)) {
+              tma_store_2d(&p.o, col, y0, pad);
+              bulk_commit();
+            }
+          }
         } else
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
-          if (have_acc) {
+          if (have_acc && !(p.debug & 2)) {
             tmem_ld_32x32(tacc + c * 32, r);
             tmem_ld_wait();
           } else {
@@ -539,7 +615,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
           const int col = col_base + c * 32;
-          if (!row_ok || col >= p.N) continue;
+          if (!row_ok || col >= p.N || (p.debug & 1)) continue;
           if constexpr (EPI == EPI_F32) {
             // unreachable: the fp32 epilogue is the transposed loop below
           } else {
@@ -634,7 +710,7 @@ static int make_map_f32(CUtensorMap* m, const void* base, int64_t rows, int64_t 
 
 // 2-D bf16 tensor [rows][cols] (row stride ld elements), box [box_rows][box_cols], 128B swizzle.
 static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld,
-                    int box_cols, int box_rows) {
+                    int box_cols, int box_rows, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeFn enc = (EncodeFn)driver_tensor_map_encode();
   if (!enc) return fail(-10, "CUDA driver entry cuTensorMapEncodeTiled not available");
   if (((uintptr_t)base & 15) != 0 || (ld * 2) % 16 != 0)
@@ -644,16 +720,16 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(-12, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return 0;
 }
 
 // CTA-pair launch: clusters of two CTAs, one pair per two SMs.
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
-  auto kern = ep_grouped_gemm_kernel<false, A_MN, B_MN, EPI, true>;
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true>;
   static bool configured = false;
   if (!configured) {
     MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM2));
@@ -740,6 +816,8 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       if (d->out[1] == nullptr) return fail(-8, "wgrad: groups >= split need a slot grad tensor");
       if ((rc = make_map_f32(&kp.c[1], d->out[1], (int64_t)(d->ngroups - d->split) * d->Mw, d->N, d->ldc))) return rc;
     }
+    if (d->two_cta != 0 && grid >= 2 && d->Mw % (2 * BM) == 0)
+      return launch_gemm2<true, true, EPI_F32, true>(kp, grid, stream);
     return launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
   }
   // A reduction tail is legal: the TMA loads zero-fill A beyond K, which also cancels whatever
@@ -762,6 +840,13 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
         if ((rc = make_map(&kp.b2[s][al], base, rows, d->K, d->ldb, BK, BN / 2))) return rc;
       }
     }
+  // output maps of the staged epilogues (plain stores remain for unaligned outputs and for the
+  // warps whose 32 rows straddle the end of a group)
+  // The SwiGLU epilogue keeps plain stores: staging its three outputs measured no faster.
+  if (d->epi == EPI_BF16 && (d->ldc * 2) % 16 == 0 && ((uintptr_t)d->out[0] & 15) == 0) {
+    if ((rc = make_map(&kp.o, d->out[0], d->a_rows, d->N, d->ldc, 64, 32))) return rc;
+    kp.tma_out = (d->debug & 16) ? 0 : 1;
+  }
   const bool two = d->two_cta != 0 && grid >= 2;
   if (d->epi == EPI_SWIGLU) {
     if (!d->b_mn) return fail(-6, "swiglu epilogue expects MN-major weights");

@@ -73,17 +73,31 @@ def check_status(device="cuda") -> None:
 
 
 DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
-# CTA pairs (tcgen05 cta_group::2, clusters of two CTAs sharing each B tile) for the token-major
-# GEMMs: ``MOONEP_B200_TWO_CTA=1``.  The variant is numerically verified but its barrier round
-# trip across the pair currently leaves the tensor pipe idle half of the time (0.69 vs
-# 1.29 PFLOP/s), so the single-CTA kernel stays the default.
-TWO_CTA = int(__import__("os").environ.get("MOONEP_B200_TWO_CTA", "0"))
+# CTA pairs (tcgen05 cta_group::2: clusters of two CTAs issue one 256-row MMA and each stages only
+# half of the B tile, which cuts the shared-memory reads per MMA from 12 KB to 8 KB, the limit of
+# the single-CTA kernel) for the token-major GEMMs.  ``MOONEP_B200_TWO_CTA``: ``auto`` (default)
+# uses pairs for launches that own the whole GPU and the single-CTA kernel for launches with a
+# CTA limit (those run next to a copy kernel, which may leave SMs without a free partner);
+# ``1`` always, ``0`` never.
+_two = __import__("os").environ.get("MOONEP_B200_TWO_CTA", "auto").strip().lower()
+TWO_CTA = {"auto": 2, "": 2}.get(_two, None)
+if TWO_CTA is None:
+    TWO_CTA = int(_two)
+PAIR_MIN_AVG_ROWS = 768
 
 
 def _launch(d: _GemmDesc) -> None:
     global _checked_layout
     d.debug = DEBUG_MODE
-    d.two_cta = TWO_CTA
+    if TWO_CTA == 2:
+        # token-major: a pair covers 256 rows of ONE group, so short groups would leave the second
+        # CTA idle; the host only knows the average (over the local groups, the slot groups hold
+        # rows taken from those).  Weight-grad tiles split the weight rows instead, but with short
+        # groups (a few k-blocks per tile) the pair's extra hand-shakes cost more than they save.
+        local_groups = max(1, min(d.ngroups, d.split))
+        d.two_cta = int(d.grid == 0 and d.total_rows >= PAIR_MIN_AVG_ROWS * local_groups)
+    else:
+        d.two_cta = TWO_CTA
     if not _checked_layout:
         assert nat.call("mep_gemm_desc_bytes") == ctypes.sizeof(_GemmDesc), "GemmDesc layout mismatch"
         _checked_layout = True

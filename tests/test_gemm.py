@@ -142,3 +142,36 @@ def test_cta_pair_variant_matches(b_mn, monkeypatch):
     two = run()
     for a, b in zip(one, two):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_cta_pair_weight_grad_matches(accumulate, monkeypatch):
+    """Weight-grad tiles of a CTA pair (256 weight rows, each CTA 128 of them and half of the B
+    tile) are bit-identical to the single-CTA kernel's, with local and slot outputs."""
+    from moonep_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(11)
+    groups = [192, 64, 0, 320, 128, 0]
+    ends, rows = _mk(groups)
+    M, N, split = 512, 320, 4
+    a = torch.randn(rows, M, device="cuda", generator=g).bfloat16()
+    b = torch.randn(rows, N, device="cuda", generator=g).bfloat16()
+    base_l = torch.randn(split, M, N, device="cuda", generator=g)
+    base_s = torch.randn(len(groups) - split, M, N, device="cuda", generator=g)
+    res = []
+    for two in (0, 1):
+        monkeypatch.setattr(gemm, "TWO_CTA", two)
+        gl, gs = base_l.clone(), base_s.clone()
+        gemm.wgrad(a, b, ends, gl, grad_slot=gs, split=split, accumulate=accumulate)
+        res.append((gl, gs))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    start = 0
+    for i, n in enumerate(groups):
+        want = a[start:start + n].float().t() @ b[start:start + n].float()
+        got = res[1][0][i] if i < split else res[1][1][i - split]
+        base = base_l[i] if i < split else base_s[i - split]
+        if accumulate:
+            want = want + base
+        elif n == 0 and i >= split:
+            want = base                       # empty slot groups are left untouched
+        _close(got, want, tol=5e-3)
+        start += n
