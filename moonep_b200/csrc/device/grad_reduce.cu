@@ -205,7 +205,7 @@ static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, cudaStream_t str
     configured = smem;
   }
   dim3 grid(c.num_sms_weights, c.Rv());
-  MEP_CUDA_OK(launch_coop((const void*)ep_grad_reduce_kernel<ST>, grid, dim3(GR_THREADS), smem, stream, p));
+  MEP_CUDA_OK(launch_coop_paired((const void*)ep_grad_reduce_kernel<ST>, grid, dim3(GR_THREADS), smem, stream, p));
   return 0;
 }
 

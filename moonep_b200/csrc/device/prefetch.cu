@@ -172,7 +172,7 @@ static int launch_prefetch_t(const BufferCtx& c, PrefetchParams& p, cudaStream_t
     configured = smem;
   }
   dim3 grid(c.num_sms_weights, c.Rv());
-  MEP_CUDA_OK(launch_coop((const void*)ep_prefetch_kernel<ST>, grid, dim3(PF_THREADS), smem, stream, p));
+  MEP_CUDA_OK(launch_coop_paired((const void*)ep_prefetch_kernel<ST>, grid, dim3(PF_THREADS), smem, stream, p));
   return 0;
 }
 

@@ -64,4 +64,30 @@ inline cudaError_t launch_coop(const void* kernel, dim3 grid, dim3 block, size_t
   return cudaLaunchCooperativeKernel(kernel, grid, block, args, smem, stream);
 }
 
+// Same, but the CTAs are placed as clusters of two (x-neighbours share one TPC).  The copy kernels
+// that run NEXT TO a CTA-pair GEMM use it: they then occupy whole SM pairs, so every SM they leave
+// free still has a free partner for a GEMM pair, whichever kernel the hardware places first.
+// The kernels themselves use no cluster feature.  Odd grids fall back to the plain launch.
+template <class Params>
+inline cudaError_t launch_coop_paired(const void* kernel, dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, Params& params) {
+  if (grid.x % 2 != 0) return launch_coop(kernel, grid, block, smem, stream, params);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 2;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  void* args[] = {(void*)&params};
+  return cudaLaunchKernelExC(&cfg, kernel, args);
+}
+
 }  // namespace mep

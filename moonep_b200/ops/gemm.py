@@ -75,10 +75,10 @@ def check_status(device="cuda") -> None:
 DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
 # CTA pairs (tcgen05 cta_group::2: clusters of two CTAs issue one 256-row MMA and each stages only
 # half of the B tile, which cuts the shared-memory reads per MMA from 12 KB to 8 KB, the limit of
-# the single-CTA kernel) for the token-major GEMMs.  ``MOONEP_B200_TWO_CTA``: ``auto`` (default)
-# uses pairs for launches that own the whole GPU and the single-CTA kernel for launches with a
-# CTA limit (those run next to a copy kernel, which may leave SMs without a free partner);
-# ``1`` always, ``0`` never.
+# the single-CTA kernel).  ``MOONEP_B200_TWO_CTA``: ``auto`` (default) uses pairs when the groups
+# are long enough on average (see ``_launch``); ``1`` always, ``0`` never.  A launch with a CTA
+# limit (one that runs next to a copy kernel) needs an even limit; the copy kernels are placed
+# as SM pairs too, so the SMs they leave free can all be paired.
 _two = __import__("os").environ.get("MOONEP_B200_TWO_CTA", "auto").strip().lower()
 TWO_CTA = {"auto": 2, "": 2}.get(_two, None)
 if TWO_CTA is None:
@@ -95,7 +95,7 @@ def _launch(d: _GemmDesc) -> None:
         # rows taken from those).  Weight-grad tiles split the weight rows instead, but with short
         # groups (a few k-blocks per tile) the pair's extra hand-shakes cost more than they save.
         local_groups = max(1, min(d.ngroups, d.split))
-        d.two_cta = int(d.grid == 0 and d.total_rows >= PAIR_MIN_AVG_ROWS * local_groups)
+        d.two_cta = int(d.grid % 2 == 0 and d.total_rows >= PAIR_MIN_AVG_ROWS * local_groups)
     else:
         d.two_cta = TWO_CTA
     if not _checked_layout:
