@@ -45,6 +45,9 @@ def parse():
                     help="CTAs of prefetch_weight / reduce_grad, which run next to the GEMMs")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="down GEMM into the shard + pull combine instead of the push epilogue")
+    ap.add_argument("--no-fused-sgd", action="store_true",
+                    help="store fp32 weight grads and run the SGD kernel over all experts, instead of "
+                         "applying SGD in the weight-grad epilogues (bit-identical results)")
     ap.add_argument("--experts", type=int, default=E,
                     help="total experts; anything but 256 is a profiling shape, not the benchmark")
     return ap.parse_args()
@@ -166,6 +169,8 @@ def run_ours(args):
     else:
         bias, mv = None, 0.0
     layer.router_bias = bias
+    if not args.no_fused_sgd:
+        layer.fuse_sgd(args.lr)
 
     def step(x):
         x = x.detach().requires_grad_(True)
@@ -291,7 +296,10 @@ def run_ours(args):
                    "global_batch": tokens, "seq_len": s, "parallelism": f"ep{R}",
                    "tokens_per_rank": s, "token_padding": TOKEN_PADDING, "num_sms_comm": buf.num_sms, "num_sms_weight_ops": buf.num_sms_weights,
                    "maxvio_target": args.maxvio, "maxvio_achieved": mv,
-                   "step": "forward + backward + SGD update, fp32 weight grads",
+                   "step": "forward + backward + SGD update" + (
+                       ", fp32 weight grads stored" if args.no_fused_sgd else
+                       ", SGD applied in the weight-grad epilogues (fp32 accumulators; experts with "
+                       "replicas store fp32 grads, reduce them home, then update)"),
                    "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",
                    "cuda_graph": graphed,
                    "l2": "working set per step (>= 8 GB of weights, grads and activations) exceeds the 126 MB L2; no explicit flush"},

@@ -546,10 +546,20 @@ class Buffer:
         on their streams before calling are visible; the reference leaves that to the caller.
         ``zero_consumed=False`` skips the final clearing for callers whose next backward pass
         overwrites the slots instead of accumulating into them."""
+        return self.reduce_grad_tensors(
+            plan, [local_gate_grad, local_up_grad, local_down_grad],
+            [gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer], async_finish,
+            entry_sync=entry_sync, zero_consumed=zero_consumed)
+
+    def reduce_grad_tensors(self, plan: CommPlan, locals_, pools, async_finish: bool = False, *,
+                            entry_sync: bool = True, zero_consumed: bool = True):
+        """``reduce_grad`` for any subset of projections: ``locals_[i]`` ``[epn, ...]`` fp32 and its
+        ``[R, epn, ...]`` reduce buffer ``pools[i]``.  A training loop that finishes the down
+        projection's weight grads long before the gate/up ones can send them home early."""
         self._require()
         assert plan is not None, "plan is required"
-        locals_ = [local_gate_grad, local_up_grad, local_down_grad]
-        pools = [gate_reduce_buffer, up_reduce_buffer, down_reduce_buffer]
+        locals_, pools = list(locals_), list(pools)
+        assert len(locals_) == len(pools) and len(locals_) >= 1
         for t in locals_ + pools:
             assert t.dtype == torch.float32, "grads and reduce buffers must be fp32"
         n, lp, pp, eb, rs = self._pool_args(locals_, pools, "reduce_grad")

@@ -141,10 +141,14 @@ ep_swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dact, const __nv_bfloat16
 
 // ---- SGD: w(bf16) -= lr * g(fp32) ----------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-ep_sgd_kernel(__nv_bfloat16* __restrict__ w, const float* __restrict__ g, long long n, float lr) {
+ep_sgd_kernel(__nv_bfloat16* __restrict__ w, const float* __restrict__ g, long long n, float lr,
+              const int32_t* __restrict__ only, long long vec_per_expert) {
   const long long nvec = n / 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
+  const float nlr = -lr;
   for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    // `only`: per-expert flags; experts with a zero flag were already updated elsewhere
+    if (only != nullptr && only[v / vec_per_expert] == 0) continue;
     uint4 w4 = reinterpret_cast<uint4*>(w)[v];
     float4 g0 = reinterpret_cast<const float4*>(g)[2 * v], g1 = reinterpret_cast<const float4*>(g)[2 * v + 1];
     __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w4);
@@ -152,12 +156,12 @@ ep_sgd_kernel(__nv_bfloat16* __restrict__ w, const float* __restrict__ g, long l
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float2 x = __bfloat1622float2(w2[i]);
-      w2[i] = __floats2bfloat162_rn(x.x - lr * gg[2 * i], x.y - lr * gg[2 * i + 1]);
+      w2[i] = __floats2bfloat162_rn(__fmaf_rn(nlr, gg[2 * i], x.x), __fmaf_rn(nlr, gg[2 * i + 1], x.y));
     }
     reinterpret_cast<uint4*>(w)[v] = w4;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (long long i = nvec * 8; i < n; ++i) w[i] = __float2bfloat16(__bfloat162float(w[i]) - lr * g[i]);
+    for (long long i = nvec * 8; i < n; ++i) w[i] = __float2bfloat16(__fmaf_rn(nlr, g[i], __bfloat162float(w[i])));
 }
 
 }  // namespace mep
@@ -214,7 +218,21 @@ int mep_sgd_update(void* w, const float* g, long long n, float lr, cudaStream_t 
   long long blocks = (nvec + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
-  ep_sgd_kernel<<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)w, g, n, lr);
+  ep_sgd_kernel<<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)w, g, n, lr, nullptr, 1);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Same update, restricted to the experts whose flag is non-zero: w and g are [experts][elems].
+int mep_sgd_update_masked(void* w, const float* g, long long experts, long long elems, const int32_t* only,
+                          float lr, cudaStream_t stream) {
+  if (((uintptr_t)w | (uintptr_t)g) % 16 != 0 || elems % 8 != 0)
+    return fail(-1, "sgd: tensors must be 16-byte aligned and elems a multiple of 8");
+  long long nvec = experts * elems / 8;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  ep_sgd_kernel<<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)w, g, experts * elems, lr, only, elems / 8);
   MEP_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -74,6 +74,13 @@ struct GemmKParams {
   int debug;
   int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
   int tma_out; // outputs are 16-byte aligned: whole 32-row blocks leave through TMA stores
+  // weight grad fused with the SGD step: a local expert's tile is applied straight to its bf16
+  // weights, w = bf16(w - lr * acc), instead of being stored as an fp32 grad.  Experts whose
+  // sgd_keep flag is set (they have replicas elsewhere, whose grads must be added first) and the
+  // slot groups are still written as fp32 grads.
+  __nv_bfloat16* sgd_w;
+  const int32_t* sgd_keep;
+  float sgd_lr;
   void* out[3];
   const float* row_scale;
   long long ldc;
@@ -138,6 +145,8 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
     t.n0 = ni * BN;
     t.num_kb = (t.rows + BK - 1) / BK;
     if (t.rows <= 0 && t.g >= p.zero_empty_below) t.valid = false;
+    if (t.rows <= 0 && p.sgd_w != nullptr && t.g < p.split &&
+        (p.sgd_keep == nullptr || p.sgd_keep[t.g] == 0)) t.valid = false;   // zero grad: nothing to apply
     if (t.g < p.g_begin) t.valid = false;
   } else {
     // largest g with prefix[g] * n_tiles_n <= id
@@ -370,6 +379,18 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
       if (!t.valid) continue;
       const int acc = tile_n & 1;
+      bool sgd_fuse = false;
+      if constexpr (WGRAD && EPI == EPI_F32) {
+        sgd_fuse = p.sgd_w != nullptr && t.alloc == 0 &&
+                   (p.sgd_keep == nullptr || p.sgd_keep[t.g_local] == 0);
+        if (sgd_fuse && t.n0 < p.N) {
+          // the tile's weights are needed only once its MMAs are done: pull this lane's row
+          // (up to 256 bf16) into L2 while the main loop runs
+          const __nv_bfloat16* wr = p.sgd_w + ((long long)t.g_local * p.Mw + t.m0 + r_in_tile) * p.ldc + t.n0;
+          const uint32_t bytes = (uint32_t)min(BN, p.N - t.n0) * 2u;
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wr), "r"(bytes) : "memory");
+        }
+      }
       if (!gemm_wait(&acc_full[acc], (uint32_t)(tile_n >> 1) & 1u, abortp, p, 4)) break;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN + ((uint32_t)(q * 32) << 16);
@@ -503,6 +524,64 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           uint8_t* pad = reinterpret_cast<uint8_t*>(s_epi) + q * 4096;
           const int y0 = t.g_local * p.Mw + t.m0 + q * 32;
           const CUtensorMap* cmap = &p.c[t.alloc];
+          if (sgd_fuse) {
+            // Each 32 x 32 fp32 block is staged in the pad as below, then re-read row-wise so
+            // that 4 lanes cover 64 contiguous bytes of one weight row: every load / store
+            // instruction touches 8 rows x 64 B in whole sectors.  The weights of block c+1 are
+            // requested before block c is processed (they already sit in L2).
+            __nv_bfloat16* wq = p.sgd_w + ((long long)t.g_local * p.Mw + t.m0 + q * 32) * p.ldc + col_base;
+            const int rsel = lane >> 2, ch = lane & 3;
+            const float nlr = -p.sgd_lr;
+            uint4 wn[4];
+            auto load_w = [&](int c, uint4* dst) {
+              const bool ok = col_base + c * 32 + ch * 8 < p.N;
+#pragma unroll
+              for (int it = 0; it < 4; ++it)
+                dst[it] = ok ? *reinterpret_cast<const uint4*>(wq + (long long)(it * 8 + rsel) * p.ldc + c * 32 + ch * 8)
+                             : make_uint4(0u, 0u, 0u, 0u);
+            };
+            load_w(0, wn);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+              if (col_base + c * 32 >= p.N) break;
+              uint32_t r[32];
+              if (!(p.debug & 2)) {
+                tmem_ld_32x32(tacc + c * 32, r);
+                tmem_ld_wait();
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
+              uint4 wc[4];
+#pragma unroll
+              for (int it = 0; it < 4; ++it) wc[it] = wn[it];
+              if (c + 1 < BN / 32) load_w(c + 1, wn);
+              if (lane == 0) bulk_wait_read<0>();     // a TMA store of an earlier tile may still read the pad
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(pad + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              __syncwarp();
+              const bool ok = col_base + c * 32 + ch * 8 < p.N;
+#pragma unroll
+              for (int it = 0; it < 4; ++it) {
+                const int rr = it * 8 + rsel;
+                const float4 g0 = *reinterpret_cast<const float4*>(pad + rr * 128 + (((2 * ch) ^ (rr & 7)) << 4));
+                const float4 g1 = *reinterpret_cast<const float4*>(pad + rr * 128 + (((2 * ch + 1) ^ (rr & 7)) << 4));
+                const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                uint4 w4 = wc[it];
+                __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w4);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 x = __bfloat1622float2(w2[i]);
+                  w2[i] = __floats2bfloat162_rn(__fmaf_rn(nlr, gg[2 * i], x.x), __fmaf_rn(nlr, gg[2 * i + 1], x.y));
+                }
+                if (ok && !(p.debug & 1))
+                  *reinterpret_cast<uint4*>(wq + (long long)rr * p.ldc + c * 32 + ch * 8) = w4;
+              }
+            }
+          } else
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
@@ -684,6 +763,10 @@ struct GemmDesc {
   int64_t push_rank_stride;
   int32_t push_entries, push_ranks;
   int32_t two_cta, pad2_;
+  void* sgd_w;
+  const int32_t* sgd_keep;
+  float sgd_lr;
+  int32_t pad3_;
 };
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -809,6 +892,12 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
     if ((rc = make_map(&kp.b[0][0], d->b[0][0], d->a_rows, d->N, d->ldb, 64, BK))) return rc;
     kp.a[1] = kp.a[0]; kp.b[0][1] = kp.b[1][0] = kp.b[1][1] = kp.b[0][0];
     if (d->epi != EPI_F32) return fail(-3, "wgrad writes fp32");
+    if (d->sgd_w != nullptr) {
+      if (d->accumulate) return fail(-13, "wgrad: the fused SGD step cannot accumulate into existing grads");
+      if (d->N % 8 != 0 || ((uintptr_t)d->sgd_w & 15) != 0)
+        return fail(-14, "wgrad: the fused SGD step needs N %% 8 == 0 and 16-byte aligned weights");
+      kp.sgd_w = (__nv_bfloat16*)d->sgd_w; kp.sgd_keep = d->sgd_keep; kp.sgd_lr = d->sgd_lr;
+    }
     const int n_local = d->split < d->ngroups ? d->split : d->ngroups;
     if ((rc = make_map_f32(&kp.c[0], d->out[0], (int64_t)n_local * d->Mw, d->N, d->ldc))) return rc;
     kp.c[1] = kp.c[0];

@@ -135,33 +135,59 @@ class _MoEFn(torch.autograd.Function):
         with tr.span("b.down_dgrad"):
             d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split)
         acc = layer.accumulate_grads
+        fused_lr = layer.fused_sgd_lr
+        do_reduce = have_slots and bool(pools.reduce)
+        sgd = lambda w: None
+        if fused_lr is not None:
+            # optimizer step inside the weight-grad epilogues.  Experts that have replicas on
+            # other ranks keep an fp32 grad (the replicas' grads are added first, sgd_step then
+            # updates only those); every other local expert is updated in place right here.
+            assert not acc, "the fused SGD step cannot be combined with grad accumulation"
+            keep = None
+            if do_reduce:
+                etc = plan.experts_to_copy.reshape(-1).long()
+                mine = (etc >= 0) & (etc // buf.epn == buf.rank)
+                keep = torch.zeros(buf.epn + 1, dtype=torch.int32, device=etc.device)
+                keep.index_fill_(0, torch.where(mine, etc % buf.epn, etc.new_full((), buf.epn)), 1)
+                keep = keep[:buf.epn]
+            layer._sgd_keep = keep
+            sgd = lambda w: (w, fused_lr, keep)
         with tr.span("b.wgrad_down"):
-            gemm.wgrad(d_out, act, cu, layer.g_down, grad_slot=gslot("down"), split=split, accumulate=acc)
+            gemm.wgrad(d_out, act, cu, layer.g_down, grad_slot=gslot("down"), split=split, accumulate=acc,
+                       sgd=sgd(layer.w_down))
         with tr.span("b.swiglu_bwd"):
             d_gate, d_up, d_scale = ew.swiglu_bwd(d_act, gate, up, w_nvs, rows_ptr=cu[-1:])
-        with tr.span("b.wgrad_gateup"):
-            gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
-            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
-        # the replicas' weight grads travel home on the comm stream while this stream computes dX
         ev_r = None
-        if have_slots and pools.reduce:
-            ev_r = buf.reduce_grad(plan, async_finish=True, local_gate_grad=layer.g_gate,
-                                   local_up_grad=layer.g_up, local_down_grad=layer.g_down,
-                                   gate_reduce_buffer=pools.reduce["gate"], up_reduce_buffer=pools.reduce["up"],
-                                   down_reduce_buffer=pools.reduce["down"],
-                                   zero_consumed=layer.accumulate_grads)   # overwritten next step otherwise
+        zc = layer.accumulate_grads            # the slots are overwritten next step otherwise
+        if fused_lr is None:
+            with tr.span("b.wgrad_gateup"):
+                gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
+                gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
+            # the replicas' weight grads travel home on the comm stream while this stream computes dX
+            if do_reduce:
+                ev_r = buf.reduce_grad(plan, async_finish=True, local_gate_grad=layer.g_gate,
+                                       local_up_grad=layer.g_up, local_down_grad=layer.g_down,
+                                       gate_reduce_buffer=pools.reduce["gate"], up_reduce_buffer=pools.reduce["up"],
+                                       down_reduce_buffer=pools.reduce["down"], zero_consumed=zc)
+        elif do_reduce:
+            # fused SGD changes w_gate / w_up in their weight-grad epilogues, so dX (which reads
+            # them) comes first; meanwhile only the down projection's grads can travel home
+            ev_r = buf.reduce_grad_tensors(plan, [layer.g_down], [pools.reduce["down"]], async_finish=True,
+                                           zero_consumed=zc)
         grid = layer.overlap_grid() if ev_r is not None else 0
         # dispatch backward = combine; the scalar path returns d(route weights) as [S, K]
         if layer.fused_combine:
             with tr.span("b.gateup_dgrad_push"):
                 gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
                                   wu_slot=slot("up"), split=split, push=buf.push_target(plan), grid=grid)
+            ev_r = _MoEFn._late_wgrads(layer, plan, hidden, d_gate, d_up, cu, gslot, split, ev_r, do_reduce, sgd)
             with tr.span("b.combine_pushed"):
                 dx, dw_sk = buf.combine_pushed(plan, d_scale)
         else:
             shard = buf.hidden_nvsh_buffer_view
             gemm.gateup_dgrad(d_gate, d_up, layer.w_gate, layer.w_up, cu, wg_slot=slot("gate"),
                               wu_slot=slot("up"), split=split, out=shard, grid=grid)
+            ev_r = _MoEFn._late_wgrads(layer, plan, hidden, d_gate, d_up, cu, gslot, split, ev_r, do_reduce, sgd)
             dx, dw_sk, _ = buf.combine(plan, shard, d_scale, zero_copy=True)
         # router backward
         with tr.span("b.router"):
@@ -173,6 +199,24 @@ class _MoEFn(torch.autograd.Function):
             with tr.span("b.wait_reduce_grad"):
                 torch.cuda.current_stream().wait_event(ev_r)      # grads are complete for the optimizer
         return dx, None
+
+    @staticmethod
+    def _late_wgrads(layer, plan, hidden, d_gate, d_up, cu, gslot, split, ev_r, do_reduce, sgd):
+        """Fused-SGD order only: the gate / up weight grads (which update the weights in their
+        epilogues) run after dX; their replicas' grads then travel home under the combine and the
+        router backward.  Returns the event that covers every reduce launched so far."""
+        if layer.fused_sgd_lr is None:
+            return ev_r
+        with layer.tracer.span("b.wgrad_gateup"):
+            gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split,
+                       sgd=sgd(layer.w_gate))
+            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, sgd=sgd(layer.w_up))
+        if do_reduce:
+            pools = layer.pools
+            ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_gate, layer.g_up],
+                                                 [pools.reduce["gate"], pools.reduce["up"]], async_finish=True,
+                                                 zero_consumed=layer.accumulate_grads)
+        return ev_r
 
 
 class MoELayer:
@@ -187,6 +231,10 @@ class MoELayer:
         self.buf, self.pools, self.Hp = buf, pools, Hp
         self.training, self.accumulate_grads = train, False
         self.fused_combine = fused_combine
+        # set to a learning rate to run the SGD step of the expert weights inside the weight-grad
+        # epilogues of the next backward pass (see ``fuse_sgd``)
+        self.fused_sgd_lr: Optional[float] = None
+        self._sgd_keep = None
         self.tracer = NULL_TRACER
         if fused_combine:
             buf.enable_push()
@@ -221,11 +269,29 @@ class MoELayer:
         assert x.dtype == torch.bfloat16 and tuple(x.shape) == (self.buf.S, self.buf.H)
         return _MoEFn.apply(x.contiguous(), self)
 
+    def fuse_sgd(self, lr: Optional[float]) -> None:
+        """Plain SGD fused into backward: with a learning rate set, the weight-grad kernels apply
+        ``w = bf16(w - lr * grad)`` to every local expert straight from their accumulators, so the
+        fp32 grad is neither written nor read back (12 -> 4 bytes of HBM traffic per parameter).
+        Experts that have replicas on other ranks this step still store their grad, receive the
+        replicas' grads through ``reduce_grad`` and are updated by ``sgd_step``, which in this
+        mode touches only them and the router.  The results are bit-identical to the unfused
+        step.  ``grads()`` of the fused experts is stale in this mode; ``None`` switches it off
+        (needed for grad accumulation or any optimizer other than plain SGD)."""
+        self.fused_sgd_lr = None if lr is None else float(lr)
+
     def sgd_step(self, lr: float) -> None:
         """``w -= lr * grad`` on every parameter (the router grad is averaged over the group by
         the caller if it wants data-parallel semantics; experts are rank-private)."""
         with self.tracer.span("sgd"):
             ew.sgd_update_(self.w_router, self.g_router[0], lr)
+            if self.fused_sgd_lr is not None:
+                assert float(lr) == self.fused_sgd_lr, "fuse_sgd() and sgd_step() disagree on the learning rate"
+                if self._sgd_keep is None:
+                    return                              # every expert was updated in backward
+                for w, g in ((self.w_gate, self.g_gate), (self.w_up, self.g_up), (self.w_down, self.g_down)):
+                    ew.sgd_update_(w, g, lr, only=self._sgd_keep)
+                return
             ew.sgd_update_(self.w_gate, self.g_gate, lr)
             ew.sgd_update_(self.w_up, self.g_up, lr)
             ew.sgd_update_(self.w_down, self.g_down, lr)

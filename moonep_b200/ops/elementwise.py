@@ -12,6 +12,7 @@ nat.declare("mep_router_topk", I, [P, P, I, I, I, P, P, P, P])
 nat.declare("mep_router_topk_bwd", I, [P, P, P, I, I, I, P, P])
 nat.declare("mep_swiglu_bwd", I, [P, P, P, P, P, I, I, P, P, P, P])
 nat.declare("mep_sgd_update", I, [P, P, L, F, P])
+nat.declare("mep_sgd_update_masked", I, [P, P, L, L, P, F, P])
 
 
 def _st():
@@ -63,8 +64,14 @@ def swiglu_bwd(dact, gate, up, row_scale=None, rows_ptr=None, want_dscale=True):
     return dgate, dup, dscale
 
 
-def sgd_update_(w: torch.Tensor, g: torch.Tensor, lr: float) -> None:
-    """In place ``w(bf16) -= lr * g(fp32)``."""
+def sgd_update_(w: torch.Tensor, g: torch.Tensor, lr: float, only: torch.Tensor = None) -> None:
+    """In place ``w(bf16) = bf16(w - lr * g(fp32))``.  ``only`` (int32 ``[experts]``, with ``w`` and
+    ``g`` shaped ``[experts, ...]``) restricts the update to the experts whose flag is non-zero."""
     assert w.dtype == torch.bfloat16 and g.dtype == torch.float32 and w.numel() == g.numel()
     assert w.is_contiguous() and g.is_contiguous()
-    _rc(nat.call("mep_sgd_update", w.data_ptr(), g.data_ptr(), w.numel(), float(lr), _st()), "sgd_update")
+    if only is None:
+        _rc(nat.call("mep_sgd_update", w.data_ptr(), g.data_ptr(), w.numel(), float(lr), _st()), "sgd_update")
+        return
+    assert only.dtype == torch.int32 and only.is_cuda and only.numel() >= w.shape[0]
+    _rc(nat.call("mep_sgd_update_masked", w.data_ptr(), g.data_ptr(), w.shape[0], w[0].numel(),
+                 only.data_ptr(), float(lr), _st()), "sgd_update")

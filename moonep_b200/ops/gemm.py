@@ -48,6 +48,8 @@ class _GemmDesc(ctypes.Structure):
         ("src_info", ctypes.c_void_p), ("push_base", ctypes.c_void_p),
         ("push_rank_stride", ctypes.c_int64), ("push_entries", ctypes.c_int32),
         ("push_ranks", ctypes.c_int32), ("two_cta", ctypes.c_int32), ("pad2_", ctypes.c_int32),
+        ("sgd_w", ctypes.c_void_p), ("sgd_keep", ctypes.c_void_p), ("sgd_lr", ctypes.c_float),
+        ("pad3_", ctypes.c_int32),
     ]
 
 
@@ -234,11 +236,18 @@ def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, spli
     return dx
 
 
-def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False):
+def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False, sgd=None):
     """``grad[g] (+)= a[rows of g]^T b[rows of g]``; ``a`` [rows, M], ``b`` [rows, N], fp32 grads
     ``[G0, M, N]`` (+ slot grads for groups >= split).  Group sizes must be multiples of 64
     (padding rows must be zero in ``a`` or ``b``).  Empty groups below ``split`` are zeroed
-    unless ``accumulate``; empty slot groups are left untouched."""
+    unless ``accumulate``; empty slot groups are left untouched.
+
+    ``sgd=(weights, lr, keep)`` fuses the optimizer step into the epilogue: for every local group
+    whose int32 ``keep`` flag is zero (``keep=None``: all of them) the tile is applied to the bf16
+    ``weights`` ``[G0, M, N]`` as ``w = bf16(w - lr * grad)``, bit-identical to ``sgd_update_`` on
+    the stored grad, and ``grad_local`` is NOT written for that group.  Groups with a set flag and
+    slot groups are stored as fp32 grads as usual.  This saves writing and re-reading the fp32
+    grad (8 of the 12 bytes per parameter that weight grad + SGD move)."""
     _bf16(a, "a"), _bf16(b, "b")
     rows, M = a.shape
     N = b.shape[1]
@@ -263,6 +272,14 @@ def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulat
     else:
         assert d.split >= ngroups
     d.ldc = N
+    if sgd is not None:
+        w, lr, keep = sgd
+        _bf16(w, "weights")
+        assert not accumulate and w.is_contiguous() and w.shape == grad_local.shape and N % 8 == 0
+        d.sgd_w, d.sgd_lr = w.data_ptr(), float(lr)
+        if keep is not None:
+            assert keep.dtype == torch.int32 and keep.is_cuda and keep.numel() >= min(d.split, ngroups)
+            d.sgd_keep = keep.data_ptr()
     d.status = status_word(a.device).data_ptr()
     _launch(d)
     return grad_local

@@ -165,8 +165,29 @@ def layer_check(R, rank):
     tot = torch.tensor([used], device="cuda")
     dist.all_reduce(tot)
     all_ok(int(tot) > 0, "skewed routing must create redundant experts", f"slots used {int(tot)}")
+    # SGD fused into the weight-grad epilogues gives bit-identical weights, also for the experts
+    # whose replicas' grads come home through reduce_grad
+    names = ("w_router", "w_gate", "w_up", "w_down")
+    w0 = {n: getattr(layer, n).clone() for n in names}
+    layer.sgd_step(0.25)
+    torch.cuda.synchronize()
+    want = {n: getattr(layer, n).clone() for n in names}
+    for n in names:
+        getattr(layer, n).copy_(w0[n])
+    layer.fuse_sgd(0.25)
+    xo2 = x.clone().requires_grad_(True)
+    y2 = layer(xo2)
+    y2.backward(dy)
+    layer.sgd_step(0.25)
+    buf.check()
+    gemm.check_status()
+    same = all(torch.equal(getattr(layer, n), want[n]) for n in names)
+    same = same and torch.equal(y2, y) and torch.equal(xo2.grad, xo.grad)
+    kept = 0 if layer._sgd_keep is None else int(layer._sgd_keep.sum())
+    all_ok(same, "fused SGD step", f"weights / outputs differ from the unfused step (kept {kept})")
+    layer.fuse_sgd(None)
     if rank == 0:
-        print(f"layer R={R}: errs {errs}, prefetch slots in use {int(tot) // R}", flush=True)
+        print(f"layer R={R}: errs {errs}, prefetch slots in use {int(tot) // R}, fused SGD ok", flush=True)
     buf.destroy()
 
 

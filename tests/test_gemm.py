@@ -175,3 +175,37 @@ def test_cta_pair_weight_grad_matches(accumulate, monkeypatch):
             want = base                       # empty slot groups are left untouched
         _close(got, want, tol=5e-3)
         start += n
+
+
+@pytest.mark.parametrize("two", [0, 1])
+def test_weight_grad_fused_sgd(two, monkeypatch):
+    """``wgrad(sgd=...)`` updates the unflagged local experts exactly like wgrad + sgd_update_, stores
+    fp32 grads for flagged experts and slot groups, and leaves experts without rows alone."""
+    from moonep_b200.ops import elementwise as ew
+    from moonep_b200.ops import gemm
+    monkeypatch.setattr(gemm, "TWO_CTA", two)
+    g = torch.Generator(device="cuda").manual_seed(13)
+    groups = [192, 0, 64, 320, 128, 0]
+    ends, rows = _mk(groups)
+    M, N, split, lr = 512, 328, 4, 0.37
+    a = torch.randn(rows, M, device="cuda", generator=g).bfloat16()
+    b = torch.randn(rows, N, device="cuda", generator=g).bfloat16()
+    w0 = torch.randn(split, M, N, device="cuda", generator=g).bfloat16()
+    gl = torch.zeros(split, M, N, device="cuda")
+    gs = torch.zeros(len(groups) - split, M, N, device="cuda")
+    gemm.wgrad(a, b, ends, gl, grad_slot=gs, split=split)
+    want = w0.clone()
+    ew.sgd_update_(want, gl, lr)
+    keep = torch.tensor([0, 0, 1, 0], dtype=torch.int32, device="cuda")
+    w = w0.clone()
+    gl2 = torch.full_like(gl, 7.0)
+    gs2 = torch.full_like(gs, 7.0)
+    gemm.wgrad(a, b, ends, gl2, grad_slot=gs2, split=split, sgd=(w, lr, keep))
+    torch.cuda.synchronize()
+    for e in (0, 1, 3):
+        assert torch.equal(w[e], want[e]) and bool((gl2[e] == 7.0).all())     # applied, grad not written
+    assert torch.equal(w[1], w0[1])                                           # no rows: untouched
+    assert torch.equal(w[2], w0[2]) and torch.equal(gl2[2], gl[2])            # flagged: grad stored
+    assert torch.equal(gs2[0], gs[0]) and bool((gs2[1] == 7.0).all())         # slots: stored / empty untouched
+    ew.sgd_update_(w, gl2, lr, only=keep)
+    assert torch.equal(w, want)

@@ -65,6 +65,39 @@ def test_moe_layer_matches_reference():
     buf.destroy()
 
 
+def test_fused_sgd_step_is_bit_identical():
+    """SGD fused into the weight-grad epilogues == weight grads stored, then the SGD kernel."""
+    from moonep_b200 import Buffer
+    from moonep_b200.models.moe_layer import MoELayer
+    from moonep_b200.ops import gemm
+    S, H, Hp, K, E = 512, 256, 384, 4, 8
+    buf = Buffer(S, H, K, E, 1, num_sms=4, token_padding=64, timeout_s=5.0)
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    dy = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    bias = torch.zeros(E, device="cuda")
+    bias[3] = -100.0                                   # one expert without tokens: weights untouched
+    res = []
+    for fused in (False, True):
+        layer = MoELayer(buf, Hp, None, seed=3, init_std=0.06, router_bias=bias)
+        if fused:
+            layer.fuse_sgd(0.5)
+        xo = x.clone().requires_grad_(True)
+        y = layer(xo)
+        y.backward(dy)
+        layer.sgd_step(0.5)
+        torch.cuda.synchronize()
+        buf.check()
+        gemm.check_status()
+        res.append((y.detach().clone(), xo.grad.clone(), layer.w_gate.clone(), layer.w_up.clone(),
+                    layer.w_down.clone(), layer.w_router.clone()))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    init = MoELayer(buf, Hp, None, seed=3, init_std=0.06)
+    assert torch.equal(res[1][2][3], init.w_gate[3]) and not torch.equal(res[1][2][0], init.w_gate[0])
+    buf.destroy()
+
+
 def test_router_topk_kernel():
     from moonep_b200.ops import elementwise as ew
     g = torch.Generator(device="cuda").manual_seed(1)
