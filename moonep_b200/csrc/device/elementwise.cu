@@ -146,9 +146,14 @@ ep_sgd_kernel(__nv_bfloat16* __restrict__ w, const float* __restrict__ g, long l
   const long long nvec = n / 8;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float nlr = -lr;
-  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
-    // `only`: per-expert flags; experts with a zero flag were already updated elsewhere
-    if (only != nullptr && only[v / vec_per_expert] == 0) continue;
+  long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x, v1 = nvec;
+  if (only != nullptr) {
+    // masked form: blockIdx.y is the expert; experts with a zero flag were updated elsewhere
+    if (only[blockIdx.y] == 0) return;
+    v0 += (long long)blockIdx.y * vec_per_expert;
+    v1 = (long long)(blockIdx.y + 1) * vec_per_expert;
+  }
+  for (long long v = v0; v < v1; v += stride) {
     uint4 w4 = reinterpret_cast<uint4*>(w)[v];
     float4 g0 = reinterpret_cast<const float4*>(g)[2 * v], g1 = reinterpret_cast<const float4*>(g)[2 * v + 1];
     __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w4);
@@ -228,11 +233,13 @@ int mep_sgd_update_masked(void* w, const float* g, long long experts, long long 
                           float lr, cudaStream_t stream) {
   if (((uintptr_t)w | (uintptr_t)g) % 16 != 0 || elems % 8 != 0)
     return fail(-1, "sgd: tensors must be 16-byte aligned and elems a multiple of 8");
-  long long nvec = experts * elems / 8;
+  if (experts < 1 || experts > 65535) return fail(-2, "sgd: 1..65535 experts");
+  long long nvec = elems / 8;
   long long blocks = (nvec + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
-  ep_sgd_kernel<<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)w, g, experts * elems, lr, only, elems / 8);
+  ep_sgd_kernel<<<dim3((unsigned)blocks, (unsigned)experts), 256, 0, stream>>>(
+      (__nv_bfloat16*)w, g, 0, lr, only, nvec);
   MEP_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -52,11 +52,9 @@ constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
 constexpr int MAX_GROUPS = 1024;
-constexpr int GEMM_SMEM = GEMM_STAGES * STAGE_BYTES + 1024;
 // CTA-pair variant: each CTA stages A (16 KB) and half of B (16 KB) per k-block, six stages.
 constexpr int GEMM_STAGES2 = 6;
 constexpr int STAGE_BYTES2 = A_TILE_BYTES + B_TILE_BYTES / 2;
-constexpr int GEMM_SMEM2 = GEMM_STAGES2 * STAGE_BYTES2 + 1024;
 
 enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2, EPI_PUSH = 3 };
 
@@ -79,6 +77,7 @@ struct GemmKParams {
   // sgd_keep flag is set (they have replicas elsewhere, whose grads must be added first) and the
   // slot groups are still written as fp32 grads.
   __nv_bfloat16* sgd_w;
+  CUtensorMap wmap;        // the same weights as a [G0 * Mw][N] bf16 tensor, 32-row x 64-column boxes, 128B swizzle
   const int32_t* sgd_keep;
   float sgd_lr;
   void* out[3];
@@ -173,11 +172,22 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
   return t;
 }
 
-template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false>
+// SGD (weight grad only): the optimizer step is fused into the epilogue.  That variant gives up
+// one stage of the operand ring for a ring of weight blocks per epilogue warp (see the epilogue).
+template <bool TWO, bool SGD> __host__ __device__ constexpr int gemm_stages() { return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (SGD ? 1 : 0); }
+template <bool TWO> __host__ __device__ constexpr int sgd_ring() { return TWO ? 2 : 3; }   // 4 KB weight blocks per warp
+template <bool TWO, bool SGD> __host__ __device__ constexpr int gemm_smem() {   // dynamic shared memory
+  return gemm_stages<TWO, SGD>() * (TWO ? STAGE_BYTES2 : STAGE_BYTES) + 1024 +
+         (SGD ? 4 * sgd_ring<TWO>() * 4096 : 0);
+}
+
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false, bool SGD = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
-  constexpr int GEMM_STAGES = TWO ? GEMM_STAGES2 : mep::GEMM_STAGES;
+  static_assert(!SGD || (WGRAD && EPI == EPI_F32), "the fused SGD step belongs to the weight grad");
+  constexpr int GEMM_STAGES = gemm_stages<TWO, SGD>();
   constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
+  constexpr int WB = SGD ? sgd_ring<TWO>() : 1;
   const int crank = TWO ? (int)cluster_cta_rank() : 0;        // 0 = leader of the pair
   const int work_id0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int work_stride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -189,8 +199,13 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
   __shared__ int s_end[MAX_GROUPS];
-  __shared__ int s_prefix[MAX_GROUPS + 1];
-  __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];   // per-warp staging pad
+  __shared__ int s_prefix[WGRAD ? 1 : MAX_GROUPS + 1];
+  // per-warp staging of the fp32 epilogues: 32 x 33 floats token-major, a 4 KB swizzled block for
+  // the weight grad
+  __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];
+  // fused SGD: per epilogue warp a ring of WB 32 x 32 bf16 weight blocks (in dynamic shared
+  // memory, behind the operand stages) and their "landed" barriers
+  __shared__ __align__(8) uint64_t wbar[4][WB];
   __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
   // staging of the bf16 epilogue: per warp one 32 x 64 block (128-byte rows, 128B swizzle)
   __shared__ __align__(1024) uint8_t s_out[(!WGRAD && EPI == EPI_BF16) ? 4 * 4096 : 16];
@@ -204,6 +219,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     // leader's producer arrives on (expecting the bytes of both CTAs); no per-stage remote arrive
     for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
+    for (int a = 0; a < 4 * WB; ++a) mbar_init(&wbar[a / WB][a % WB], 1);
     mbar_fence_init();
     s_abort = 0;
   }
@@ -375,22 +391,54 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     const int q = warp & 3;
     const int r_in_tile = q * 32 + lane;
     int tile_n = 0;
+    // ---- fused SGD: weight blocks stream through this warp's ring, ahead of the tiles ----------
+    // Block k of the stream (the 32-row x 64-column blocks of this warp's rows, tile after tile,
+    // fused tiles only) lives in buffer k % WB.  The load cursor runs up to WB blocks ahead of the
+    // block being updated, across tile boundaries.  Blocks are as wide as the 128B swizzle
+    // allows: the TMA engine moves about one box row per 5 cycles per SM whatever its length
+    // (measured), so 64-byte rows cap this epilogue at half the HBM rate.
+    constexpr int WBLK = 4096, WCOLS = 64;
+    uint8_t* wring = tiles + (size_t)GEMM_STAGES * STAGE_BYTES + q * (WB * WBLK);
+    int wseq = 0, lseq = 0;                // blocks consumed / loads issued (a few thousand per launch)
+    long long lid = work_id0;              // cursor: tile id, block in tile, cached coordinates
+    int lc = 0, l_y0 = 0, l_n0 = 0;
+    bool l_have = false;
+    auto sgd_tile = [&](const Tile& u) {
+      return u.valid && u.alloc == 0 && (p.sgd_keep == nullptr || p.sgd_keep[u.g_local] == 0);
+    };
+    auto cursor_settle = [&]() {           // move to the next existing block at or after (lid, lc)
+      while (lid < total_tiles) {
+        if (!l_have) {
+          const Tile u = get_tile<WGRAD, EPI, TWO>(p, (int)lid, s_end, s_prefix, n_tiles_n, crank);
+          if (sgd_tile(u)) { l_have = true; l_y0 = u.g_local * p.Mw + u.m0 + q * 32; l_n0 = u.n0; lc = 0; }
+        }
+        if (l_have && lc < BN / WCOLS && l_n0 + lc * WCOLS < p.N) return;
+        l_have = false;
+        lid += work_stride;
+      }
+    };
+    auto issue_loads = [&]() {             // lane 0 issues; every lane tracks the cursor
+      while (lid < total_tiles && lseq < wseq + WB) {
+        if (lane == 0) {
+          uint64_t* bar = &wbar[q][lseq % WB];
+          mbar_expect_tx(bar, WBLK);
+          tma_load_2d(wring + (lseq % WB) * WBLK, &p.wmap, l_n0 + lc * WCOLS, l_y0, bar);
+        }
+        ++lseq;
+        ++lc;
+        cursor_settle();
+      }
+    };
+    if constexpr (SGD) {
+      cursor_settle();
+      issue_loads();
+    }
     for (long long id = work_id0; id < total_tiles; id += work_stride) {
       Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
       if (!t.valid) continue;
       const int acc = tile_n & 1;
       bool sgd_fuse = false;
-      if constexpr (WGRAD && EPI == EPI_F32) {
-        sgd_fuse = p.sgd_w != nullptr && t.alloc == 0 &&
-                   (p.sgd_keep == nullptr || p.sgd_keep[t.g_local] == 0);
-        if (sgd_fuse && t.n0 < p.N) {
-          // the tile's weights are needed only once its MMAs are done: pull this lane's row
-          // (up to 256 bf16) into L2 while the main loop runs
-          const __nv_bfloat16* wr = p.sgd_w + ((long long)t.g_local * p.Mw + t.m0 + r_in_tile) * p.ldc + t.n0;
-          const uint32_t bytes = (uint32_t)min(BN, p.N - t.n0) * 2u;
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(wr), "r"(bytes) : "memory");
-        }
-      }
+      if constexpr (SGD) sgd_fuse = sgd_tile(t);
       if (!gemm_wait(&acc_full[acc], (uint32_t)(tile_n >> 1) & 1u, abortp, p, 4)) break;
       tc_fence_after();
       const uint32_t tacc = tmem_base + (uint32_t)acc * BN + ((uint32_t)(q * 32) << 16);
@@ -524,63 +572,61 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           uint8_t* pad = reinterpret_cast<uint8_t*>(s_epi) + q * 4096;
           const int y0 = t.g_local * p.Mw + t.m0 + q * 32;
           const CUtensorMap* cmap = &p.c[t.alloc];
-          if (sgd_fuse) {
-            // Each 32 x 32 fp32 block is staged in the pad as below, then re-read row-wise so
-            // that 4 lanes cover 64 contiguous bytes of one weight row: every load / store
-            // instruction touches 8 rows x 64 B in whole sectors.  The weights of block c+1 are
-            // requested before block c is processed (they already sit in L2).
-            __nv_bfloat16* wq = p.sgd_w + ((long long)t.g_local * p.Mw + t.m0 + q * 32) * p.ldc + col_base;
-            const int rsel = lane >> 2, ch = lane & 3;
+          if (SGD && sgd_fuse) {
+            // Weights travel by TMA both ways: a block is 32 rows x 64 bf16 (128-byte rows, 128B
+            // swizzle); lane i owns row i of the block, exactly the accumulator row it reads from
+            // tensor memory, so no transposition is needed.  The block is updated in place,
+            // stored back, and its buffer handed to the load cursor.
             const float nlr = -p.sgd_lr;
-            uint4 wn[4];
-            auto load_w = [&](int c, uint4* dst) {
-              const bool ok = col_base + c * 32 + ch * 8 < p.N;
-#pragma unroll
-              for (int it = 0; it < 4; ++it)
-                dst[it] = ok ? *reinterpret_cast<const uint4*>(wq + (long long)(it * 8 + rsel) * p.ldc + c * 32 + ch * 8)
-                             : make_uint4(0u, 0u, 0u, 0u);
-            };
-            load_w(0, wn);
+            bool wok = true;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-              if (col_base + c * 32 >= p.N) break;
-              uint32_t r[32];
+            for (int c = 0; c < BN / WCOLS; ++c) {
+              if (col_base + c * WCOLS >= p.N) break;
+              const int b = wseq % WB;
+              uint8_t* wbuf = wring + b * WBLK;
+              uint32_t ra[32], rb[32];
               if (!(p.debug & 2)) {
-                tmem_ld_32x32(tacc + c * 32, r);
+                tmem_ld_32x32(tacc + c * WCOLS, ra);
+                tmem_ld_32x32(tacc + c * WCOLS + 32, rb);
+              }
+              if (!gemm_wait(&wbar[q][b], (uint32_t)(wseq / WB) & 1u, abortp, p, 5)) {
+                if (!(p.debug & 2)) tmem_ld_wait();
+                wok = false;
+                break;
+              }
+              if (!(p.debug & 2)) {
                 tmem_ld_wait();
               } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = 0u;
+                for (int i = 0; i < 32; ++i) ra[i] = rb[i] = 0u;
               }
-              uint4 wc[4];
 #pragma unroll
-              for (int it = 0; it < 4; ++it) wc[it] = wn[it];
-              if (c + 1 < BN / 32) load_w(c + 1, wn);
-              if (lane == 0) bulk_wait_read<0>();     // a TMA store of an earlier tile may still read the pad
-              __syncwarp();
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<uint4*>(pad + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-              __syncwarp();
-              const bool ok = col_base + c * 32 + ch * 8 < p.N;
-#pragma unroll
-              for (int it = 0; it < 4; ++it) {
-                const int rr = it * 8 + rsel;
-                const float4 g0 = *reinterpret_cast<const float4*>(pad + rr * 128 + (((2 * ch) ^ (rr & 7)) << 4));
-                const float4 g1 = *reinterpret_cast<const float4*>(pad + rr * 128 + (((2 * ch + 1) ^ (rr & 7)) << 4));
-                const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                uint4 w4 = wc[it];
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t* g = j < 4 ? ra + 8 * j : rb + 8 * (j - 4);
+                uint4* slot = reinterpret_cast<uint4*>(wbuf + lane * 128 + ((j ^ (lane & 7)) << 4));
+                uint4 w4 = *slot;
                 __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w4);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const float2 x = __bfloat1622float2(w2[i]);
-                  w2[i] = __floats2bfloat162_rn(__fmaf_rn(nlr, gg[2 * i], x.x), __fmaf_rn(nlr, gg[2 * i + 1], x.y));
+                  w2[i] = __floats2bfloat162_rn(__fmaf_rn(nlr, __uint_as_float(g[2 * i]), x.x),
+                                                __fmaf_rn(nlr, __uint_as_float(g[2 * i + 1]), x.y));
                 }
-                if (ok && !(p.debug & 1))
-                  *reinterpret_cast<uint4*>(wq + (long long)rr * p.ldc + c * 32 + ch * 8) = w4;
+                *slot = w4;
               }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (!(p.debug & 1)) {
+                  tma_store_2d(&p.wmap, col_base + c * WCOLS, y0, wbuf);
+                  bulk_commit();
+                }
+                bulk_wait_read<0>();                // the store has read the buffer: it may be refilled
+              }
+              ++wseq;
+              issue_loads();
             }
+            if (!wok) break;
           } else
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
@@ -810,9 +856,10 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
 }
 
 // CTA-pair launch: clusters of two CTAs, one pair per two SMs.
-template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false>
+template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
-  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true>;
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true, SGD>;
+  constexpr int GEMM_SMEM2 = gemm_smem<true, SGD>();
   static bool configured = false;
   if (!configured) {
     MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM2));
@@ -845,9 +892,10 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   return 0;
 }
 
-template <bool WGRAD, bool A_MN, bool B_MN, int EPI>
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool SGD = false>
 static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
-  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI>;
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, false, SGD>;
+  constexpr int GEMM_SMEM = gemm_smem<false, SGD>();
   static bool configured = false;
   if (!configured) {
     MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
@@ -897,6 +945,8 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       if (d->N % 8 != 0 || ((uintptr_t)d->sgd_w & 15) != 0)
         return fail(-14, "wgrad: the fused SGD step needs N %% 8 == 0 and 16-byte aligned weights");
       kp.sgd_w = (__nv_bfloat16*)d->sgd_w; kp.sgd_keep = d->sgd_keep; kp.sgd_lr = d->sgd_lr;
+      const int n_w = d->split < d->ngroups ? d->split : d->ngroups;
+      if ((rc = make_map(&kp.wmap, d->sgd_w, (int64_t)n_w * d->Mw, d->N, d->ldc, 64, 32))) return rc;
     }
     const int n_local = d->split < d->ngroups ? d->split : d->ngroups;
     if ((rc = make_map_f32(&kp.c[0], d->out[0], (int64_t)n_local * d->Mw, d->N, d->ldc))) return rc;
@@ -905,9 +955,12 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       if (d->out[1] == nullptr) return fail(-8, "wgrad: groups >= split need a slot grad tensor");
       if ((rc = make_map_f32(&kp.c[1], d->out[1], (int64_t)(d->ngroups - d->split) * d->Mw, d->N, d->ldc))) return rc;
     }
-    if (d->two_cta != 0 && grid >= 2 && d->Mw % (2 * BM) == 0)
-      return launch_gemm2<true, true, EPI_F32, true>(kp, grid, stream);
-    return launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
+    const bool pair = d->two_cta != 0 && grid >= 2 && d->Mw % (2 * BM) == 0;
+    if (kp.sgd_w != nullptr)
+      return pair ? launch_gemm2<true, true, EPI_F32, true, true>(kp, grid, stream)
+                  : launch_gemm<true, true, true, EPI_F32, true>(kp, grid, stream);
+    return pair ? launch_gemm2<true, true, EPI_F32, true>(kp, grid, stream)
+                : launch_gemm<true, true, true, EPI_F32>(kp, grid, stream);
   }
   // A reduction tail is legal: the TMA loads zero-fill A beyond K, which also cancels whatever
   // a MN-major B tile picks up from the next expert's rows.

@@ -207,15 +207,18 @@ class _MoEFn(torch.autograd.Function):
         router backward.  Returns the event that covers every reduce launched so far."""
         if layer.fused_sgd_lr is None:
             return ev_r
+        pools, zc = layer.pools, layer.accumulate_grads
         with layer.tracer.span("b.wgrad_gateup"):
             gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split,
                        sgd=sgd(layer.w_gate))
-            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, sgd=sgd(layer.w_up))
-        if do_reduce:
-            pools = layer.pools
-            ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_gate, layer.g_up],
-                                                 [pools.reduce["gate"], pools.reduce["up"]], async_finish=True,
-                                                 zero_consumed=layer.accumulate_grads)
+            if do_reduce:     # the gate grads travel home under the up projection's weight grad
+                ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_gate], [pools.reduce["gate"]],
+                                                     async_finish=True, zero_consumed=zc)
+            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, sgd=sgd(layer.w_up),
+                       grid=layer.overlap_grid() if do_reduce else 0)
+        if do_reduce:         # and the up grads under the combine and the router backward
+            ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
+                                                 async_finish=True, zero_consumed=zc)
         return ev_r
 
 

@@ -236,7 +236,8 @@ def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, spli
     return dx
 
 
-def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False, sgd=None):
+def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False, sgd=None,
+          grid=0):
     """``grad[g] (+)= a[rows of g]^T b[rows of g]``; ``a`` [rows, M], ``b`` [rows, N], fp32 grads
     ``[G0, M, N]`` (+ slot grads for groups >= split).  Group sizes must be multiples of 64
     (padding rows must be zero in ``a`` or ``b``).  Empty groups below ``split`` are zeroed
@@ -272,6 +273,7 @@ def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulat
     else:
         assert d.split >= ngroups
     d.ldc = N
+    d.grid = grid
     if sgd is not None:
         w, lr, keep = sgd
         _bf16(w, "weights")
