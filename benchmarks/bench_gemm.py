@@ -41,7 +41,13 @@ def main():
     ap.add_argument("--Hp", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default="")
-    ap.add_argument("--debug-mode", type=int, default=0, help="kernel timing experiment (results are wrong)")
+    ap.add_argument("--debug-mode", type=int, default=0,
+                    help="kernel timing experiment, a bit mask (results are wrong unless 0 or 16): 1 no "
+                         "epilogue stores, 2 no TMEM loads, 4 no MMAs, 8 no TMA loads, 16 plain-store epilogue")
+    ap.add_argument("--ab", action="store_true",
+                    help="interleaved A/B of the kernel variants (single CTA / CTA pair, TMA-store / plain "
+                         "epilogue, weight grad with and without the fused SGD step): best of 6 rounds each, "
+                         "run back to back so that all variants see the same clocks")
     args = ap.parse_args()
     G, rpg, H, Hp = args.groups, args.rows_per_group, args.H, args.Hp
     gemm.DEBUG_MODE = args.debug_mode
@@ -75,6 +81,8 @@ def main():
         "cublas_ref_down(torch.bmm)": (lambda: torch.bmm(act.view(G, rpg, Hp), wd.transpose(1, 2)), F),
     }
     out = {"shape": dict(groups=G, rows_per_group=rpg, H=H, Hp=Hp), "peak_tflops_measured": peak}
+    if args.ab:
+        return ab(args, ops, x, act, cu, grad, wg, out)
     for name, (fn, flops) in ops.items():
         if args.only and args.only not in name:
             continue
@@ -94,6 +102,40 @@ def main():
         ms = timeit(lambda: grad.zero_(), args.iters, flush=flush)
         out["hbm_write_only(torch zero_)"] = {"ms": round(ms, 4), "gbs": round(n * 4 / ms / 1e6, 1)}
     torch.cuda.synchronize()
+    gemm.check_status()
+    print(json.dumps(out))
+
+
+def ab(args, ops, x, act, cu, grad, w, out):
+    def run(fn, n=6):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n
+
+    variants = [("single", 0, 0), ("single_plain_epilogue", 0, 16), ("pair", 1, 0), ("pair_plain_epilogue", 1, 16)]
+    ops = dict(ops)
+    ops.pop("cublas_ref_down(torch.bmm)", None)
+    flops_w = ops["wgrad"][1]
+    ops["wgrad_fused_sgd"] = (lambda: gemm.wgrad(x, act, cu, grad, sgd=(w, 1e-6, None)), flops_w)
+    for name, (fn, flops) in ops.items():
+        if args.only and args.only not in name:
+            continue
+        vs = [v for v in variants if "wgrad" not in name or v[2] == 0]
+        for _, two, dbg in vs:
+            gemm.TWO_CTA, gemm.DEBUG_MODE = two, dbg | args.debug_mode
+            fn()
+        torch.cuda.synchronize()
+        best = {v[0]: 1e9 for v in vs}
+        for _ in range(6):
+            for v, two, dbg in vs:
+                gemm.TWO_CTA, gemm.DEBUG_MODE = two, dbg | args.debug_mode
+                best[v] = min(best[v], run(fn))
+        out[name] = {v: {"ms": round(t, 4), "tflops": round(flops / t / 1e9)} for v, t in best.items()}
+    gemm.TWO_CTA, gemm.DEBUG_MODE = 2, 0
     gemm.check_status()
     print(json.dumps(out))
 
