@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--maxvio", type=float, default=4.0)
     ap.add_argument("--lr", type=float, default=1e-3)
     ap.add_argument("--impls", default="fused,nccl")
+    ap.add_argument("--fused-sgd", action="store_true",
+                    help="apply the expert weights' SGD step inside the weight-grad kernels (peer-memory path only)")
     ap.add_argument("--graph", action="store_true",
                     help="capture the fused step in a CUDA graph (off by default: with the dense-grad NCCL "
                          "all-reduce inside the graph, process-group teardown has been seen to stall)")
@@ -85,22 +87,22 @@ def main():
         torch.cuda.reset_peak_memory_stats(dev)
         losses = []
         for i in range(args.warmup):
-            losses.append(float(model.train_step(*batches[i % 4], args.lr)))
+            losses.append(float(model.train_step(*batches[i % 4], args.lr, args.fused_sgd)))
         # The fused path has static shapes and no host synchronisation, so the whole step
         # (~2400 launches for 8 layers) replays from one CUDA graph.  The NCCL baseline cannot:
         # its all_to_all split sizes are read back to the host every layer.
-        run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr)), False
+        run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr, args.fused_sgd)), False
         if impl == "fused" and args.graph:
             try:
                 from moonep_b200.utils.graph import GraphedStep
-                gs = GraphedStep(lambda tok, tgt: model.train_step(tok, tgt, args.lr), list(batches[0]), warmup=1)
+                gs = GraphedStep(lambda tok, tgt: model.train_step(tok, tgt, args.lr, args.fused_sgd), list(batches[0]), warmup=1)
                 run_step, graphed = (lambda tok, tgt: gs(tok, tgt)), True
                 float(run_step(*batches[1]))
             except Exception as exc:  # noqa: BLE001
                 if rank == 0:
                     print(f"[bench_decoder] graph capture failed, eager: {type(exc).__name__}: {exc}",
                           file=sys.stderr, flush=True)
-                run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr)), False
+                run_step, graphed = (lambda tok, tgt: model.train_step(tok, tgt, args.lr, args.fused_sgd)), False
                 torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()

@@ -887,7 +887,18 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
     if (cudaOccupancyMaxActiveClusters(&n, kern, &probe) != cudaSuccess || n < 1) { cudaGetLastError(); n = 1 << 20; }
     max_clusters = n;
   }
-  if ((int)cfg.gridDim.x / 2 > max_clusters) cfg.gridDim = dim3((unsigned)(2 * max_clusters));
+  int use = max_clusters;
+  {
+    // a launch with a CTA limit shares the GPU with a copy kernel that is placed as SM pairs too:
+    // leave it its pairs out of what the device can hold, or this persistent grid would need a
+    // second wave
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (grid < sms && max_clusters < (1 << 20)) use = max_clusters - (sms - grid + 1) / 2;
+    if (use < 1) use = 1;
+  }
+  if ((int)cfg.gridDim.x / 2 > use) cfg.gridDim = dim3((unsigned)(2 * use));
   MEP_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, kp));
   return 0;
 }

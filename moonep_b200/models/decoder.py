@@ -182,8 +182,13 @@ class MoEDecoder(nn.Module):
     def moe_layers(self):
         return [b.moe for b in self.blocks]
 
-    def train_step(self, tokens, targets, lr):
-        """forward + backward + dense-grad all-reduce + SGD on everything; returns the loss."""
+    def train_step(self, tokens, targets, lr, fuse_expert_sgd: bool = False):
+        """forward + backward + all-reduce of the replicated parameters' grads (dense layers and
+        the MoE routers) + SGD on everything; returns the loss.  ``fuse_expert_sgd`` applies the
+        expert weights' SGD step inside the weight-grad kernels (``MoELayer.fuse_sgd``)."""
+        for m in self.moe_layers():
+            if hasattr(m, "fuse_sgd"):
+                m.fuse_sgd(lr if fuse_expert_sgd else None)
         loss = self(tokens, targets)
         loss.backward()
         dense = [p for p in self.parameters() if p.grad is not None]
@@ -197,6 +202,15 @@ class MoEDecoder(nn.Module):
                 n = p.numel()
                 p.grad.copy_(flat[off:off + n].view_as(p))
                 off += n
+            # the routers are replicated too (same seed on every rank): average their fp32 grads
+            routers = [m.g_router for m in self.moe_layers()]
+            rflat = torch.cat([g.reshape(-1) for g in routers])
+            dist.all_reduce(rflat, group=self.group)
+            rflat.div_(R)
+            off = 0
+            for g in routers:
+                g.copy_(rflat[off:off + g.numel()].view_as(g))
+                off += g.numel()
         with torch.no_grad():
             for p in dense:
                 p.add_(p.grad, alpha=-lr)
