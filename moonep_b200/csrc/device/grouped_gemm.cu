@@ -8,8 +8,9 @@
 // host synchronisation), with three warp roles:
 //   warp 0      TMA producer        (4-stage ring of 128x64 A and 256x64 B tiles, 48 KB each)
 //   warp 1      MMA issuer          (128x256x16 UMMAs, two 256-column TMEM accumulators)
-//   warps 2..5  epilogue            (TMEM -> registers -> global), overlapped with the next
-//                                   tile's main loop through the second accumulator
+//   warps 2..5  epilogue            (TMEM -> registers -> global, plain stores or staged TMA
+//                                   stores), overlapped with the next tile's main loop through
+//                                   the second accumulator
 // Modes:
 //   token-major (groups partition the rows of A and C):
 //        C[rows of g] = A[rows of g] * B[g]     B K-major ([N][K]) or MN-major ([K][N])
@@ -21,7 +22,10 @@
 //        HOME rank's staging buffer, so the transfer overlaps the math tile by tile; the home
 //        rank then only sums K local rows per token.
 //   weight-grad (groups partition the REDUCTION dimension):
-//        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output.
+//        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output by TMA
+//        store / reduce-add; or (template SGD) the optimizer step fused in: the accumulator is
+//        applied straight to the bf16 weights, w = bf16(w - lr * acc), through a per-warp TMA
+//        ring of weight blocks, for every local expert that has no replica this step.
 // Group g < split reads/writes allocation 0 (local experts), g >= split allocation 1 (this
 // rank's prefetch / reduce slots): the [2*epn] compute view never has to be contiguous.
 // CTA pairs (template TWO, clusters of two CTAs, tcgen05 cta_group::2): the leader issues
