@@ -43,8 +43,13 @@ def parse():
     ap.add_argument("--trace", action="store_true", help="also print a per-span device-time table")
     ap.add_argument("--weight-sms", type=int, default=16,
                     help="CTAs of prefetch_weight / reduce_grad, which run next to the GEMMs")
+    ap.add_argument("--comm-sms", type=int, default=0,
+                    help="CTAs of dispatch / combine (default: 32 with peers, 96 on one GPU, where they are local copies)")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="down GEMM into the shard + pull combine instead of the push epilogue")
+    ap.add_argument("--copy-dispatch-out", action="store_true",
+                    help="forward dispatch copies its rows out of the shard (instead of keeping them in a "
+                         "second shard until backward is done)")
     ap.add_argument("--no-fused-sgd", action="store_true",
                     help="store fp32 weight grads and run the SGD kernel over all experts, instead of "
                          "applying SGD in the weight-grad epilogues (bit-identical results)")
@@ -155,10 +160,11 @@ def run_ours(args):
     if R > 1:
         dist.init_process_group("nccl", device_id=dev)
     s, h, hp, k, e = (512, 1024, 512, 4, 32) if args.small else (S, H, HP, K, args.experts)
-    buf = Buffer(s, h, k, e, R, num_sms=NUM_SMS if R > 1 else 16, token_padding=TOKEN_PADDING,
+    buf = Buffer(s, h, k, e, R, num_sms=args.comm_sms or (NUM_SMS if R > 1 else 96), token_padding=TOKEN_PADDING,
                  num_sms_weights=args.weight_sms)
     pools = ExpertPools(R, e // R, h, hp, buf.group, rank) if R > 1 else None
-    layer = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine)
+    layer = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine,
+                     hidden_in_place=not args.copy_dispatch_out)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     n_batches = 4
     host = [torch.randn(s, h, generator=torch.Generator().manual_seed(1000 * rank + i)).bfloat16().pin_memory()

@@ -42,6 +42,7 @@ nat.declare("mep_sync_state_ints", I, [])
 nat.declare("mep_meta_offsets", None, [L, I, I, ctypes.POINTER(ctypes.c_int64)])
 nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
 nat.declare("mep_ctx_destroy", None, [P])
+nat.declare("mep_ctx_set_hidden", I, [P, P, L])
 nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P])
 nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, P, I, I, P])
 nat.declare("mep_launch_push_reduce", I, [P, P, L, P, L, P, P, P, P, P, I, P])
@@ -150,6 +151,7 @@ class Buffer:
             self.meta_buf, self.meta_mc = symm.create_nvl_dist_multicast_tensor(
                 (meta_ints,), torch.int32, group=self.group, device=self.device)
         self.hidden_stride = self.hidden_buf.shape[0] // R
+        self.hidden_buf2 = None
         self.meta_stride = self.meta_buf.shape[0] // R
         offs = (ctypes.c_int64 * 6)()
         nat.call("mep_meta_offsets", self.NvS, R, E, offs)
@@ -200,10 +202,39 @@ class Buffer:
     def _shape(self, *tail):
         return (self.R, *tail) if self.virtual else tuple(tail)
 
-    def _shards(self) -> torch.Tensor:
+    def _shards(self, shard: int = 0) -> torch.Tensor:
         """[Rv, NvS, H] view of the local shard(s)."""
-        hb = self.hidden_buf.view(self.R, self.hidden_stride, self.H)
+        buf = self.hidden_buf if shard == 0 else self.hidden_buf2
+        assert buf is not None, "enable_second_shard() first"
+        hb = buf.view(self.R, self.hidden_stride, self.H)
         return hb[:, : self.NvS] if self.virtual else hb[self.rank: self.rank + 1, : self.NvS]
+
+    def enable_second_shard(self) -> None:
+        """Allocates a second symmetric ``[NvS, H]`` row buffer (collective, once).  ``dispatch(...,
+        zero_copy=True, shard=1)`` then lands a forward pass's rows there and returns them in
+        place, where they stay valid while later dispatches use shard 0 (a training step's
+        backward dispatch): the copy out of the shard that ``zero_copy=False`` pays is saved.
+        The caller must be done with the rows before the next ``shard=1`` dispatch."""
+        self._require()
+        if self.hidden_buf2 is not None:
+            return
+        if self._solo:
+            self.hidden_buf2 = symm.create_local_group_tensor((self.NvS, self.H), torch.bfloat16, self.R, self.device)
+        else:
+            self.hidden_buf2 = symm.create_nvl_dist_tensor((self.NvS, self.H), torch.bfloat16, group=self.group,
+                                                           device=self.device)
+        assert self.hidden_buf2.shape[0] // self.R == self.hidden_stride
+
+    def hidden_view(self, shard: int = 0) -> torch.Tensor:
+        """``hidden_nvsh_buffer_view`` of the given shard."""
+        self._require()
+        v = self._shards(shard)
+        return v if self.virtual else v[0]
+
+    def _select_shard(self, shard: int) -> None:
+        buf = self.hidden_buf if shard == 0 else self.hidden_buf2
+        assert shard in (0, 1) and buf is not None, "shard must be 0, or 1 after enable_second_shard()"
+        self._rc(nat.call("mep_ctx_set_hidden", self._ctx, buf.data_ptr(), self.hidden_stride), "select shard")
 
     def _meta_rows(self) -> torch.Tensor:
         mb = self.meta_buf.view(self.R, self.meta_stride)
@@ -283,9 +314,10 @@ class Buffer:
     def dispatch(self, hidden_sh, route_weights_sk=None, topk_experts_sk=None,
                  tokens_per_expert=None, plan: Optional[CommPlan] = None,
                  async_finish: bool = False, *, inter_rank_sync: bool = True,
-                 zero_copy: bool = False, router_weights_zero_copy: bool = False):
+                 zero_copy: bool = False, router_weights_zero_copy: bool = False, shard: int = 0):
         """Fused permute + all-to-all.  Returns ``(hidden_nvsh[NvS,H], route_weights_nvs[NvS] |
         None, cu_seqlens[2*epn] | None, plan[, event])`` (moonep/api.py:698-836).
+        ``shard=1`` receives into the second row buffer (see ``enable_second_shard``).
 
         Without ``plan`` a fresh plan is made from ``topk_experts_sk`` / ``tokens_per_expert``.
         With ``plan`` the planner is skipped, ``cu_seqlens`` is ``None``, the same plan object is
@@ -313,9 +345,17 @@ class Buffer:
                 "plan was made by a Buffer of another shape"
 
         def run():
-            return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
-                                                    tokens_per_expert, plan, inter_rank_sync,
-                                                    zero_copy, router_weights_zero_copy)
+            if shard == 0:
+                return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
+                                                        tokens_per_expert, plan, inter_rank_sync,
+                                                        zero_copy, router_weights_zero_copy)
+            self._select_shard(shard)
+            try:
+                return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
+                                                        tokens_per_expert, plan, inter_rank_sync,
+                                                        zero_copy, router_weights_zero_copy, shard)
+            finally:
+                self._select_shard(0)
 
         if async_finish:
             out, ev = self._run_async([hidden_sh, route_weights_sk, topk_experts_sk, tokens_per_expert], run)
@@ -325,7 +365,8 @@ class Buffer:
             return (*out, ev)
         return run()
 
-    def _dispatch_on_current_stream(self, x, w, topk, tpe, plan, inter_rank_sync, zero_copy, w_zero_copy):
+    def _dispatch_on_current_stream(self, x, w, topk, tpe, plan, inter_rank_sync, zero_copy, w_zero_copy,
+                                    shard: int = 0):
         dev = x.device
         st = self._stream()
         fresh = plan is None
@@ -352,8 +393,8 @@ class Buffer:
                           int(bool(inter_rank_sync) and not fresh), int(fresh), st), "dispatch")
         self._rc(nat.call("mep_launch_expand", self._ctx, plan.link.data_ptr(),
                           plan.cu_seqlens.data_ptr(), st), "dispatch expand")
-        shard = self.hidden_nvsh_buffer_view
-        hidden = shard if zero_copy else shard.clone()
+        view = self.hidden_view(shard)
+        hidden = view if zero_copy else view.clone()
         weights = None
         if w is not None:
             wv = self.router_weight_buffer_view
@@ -610,7 +651,7 @@ class Buffer:
         finally:
             nat.call("mep_ctx_destroy", self._ctx)
             self._ctx = None
-            for name in ("meta_mc", "meta_buf", "hidden_buf", "push_buf", "wpush_buf"):
+            for name in ("meta_mc", "meta_buf", "hidden_buf", "hidden_buf2", "push_buf", "wpush_buf"):
                 t = getattr(self, name, None)
                 setattr(self, name, None)
                 if t is not None:

@@ -55,4 +55,15 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
 
 void mep_ctx_destroy(void* ctx) { delete (BufferCtx*)ctx; }
 
+// Points the context at another symmetric row buffer of the same geometry (a Buffer may own a
+// second shard so that a forward dispatch can stay in place while backward reuses the first).
+// Host-side state only: launches already issued keep the pointer they were given.
+int mep_ctx_set_hidden(void* ctx, void* hidden, int64_t hidden_stride_rows) {
+  BufferCtx* c = (BufferCtx*)ctx;
+  if (c == nullptr || hidden == nullptr) return fail(-1, "ctx: set_hidden needs a context and a buffer");
+  c->hidden = hidden;
+  c->hidden_stride = hidden_stride_rows;
+  return 0;
+}
+
 }  // extern "C"

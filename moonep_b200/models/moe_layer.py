@@ -73,7 +73,10 @@ class _MoEFn(torch.autograd.Function):
             logits = gemm.dense(x, layer.w_router)                         # [S, E] fp32
             topk, w, tpe = ew.router_topk(logits, buf.K, layer.router_bias)
         with tr.span("f.dispatch"):
-            hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
+            if layer.hidden_in_place:      # rows stay in the second shard until backward has used them
+                hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe, zero_copy=True, shard=1)
+            else:
+                hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
         pools = layer.pools
         if pools is not None and pools.prefetch:
             # the owners push the redundant experts' weights on the comm stream while this stream
@@ -227,7 +230,7 @@ class MoELayer:
 
     def __init__(self, buf: Buffer, Hp: int, pools: Optional[ExpertPools] = None, *, seed: int = 0,
                  router_bias: Optional[torch.Tensor] = None, init_std: float = 0.02,
-                 train: bool = True, fused_combine: bool = True):
+                 train: bool = True, fused_combine: bool = True, hidden_in_place: bool = False):
         assert not buf.virtual, "MoELayer runs one rank per process"
         assert buf.token_padding % 64 == 0, "the grouped GEMM needs token_padding % 64 == 0"
         assert buf.H % 128 == 0 and Hp % 64 == 0
@@ -241,6 +244,14 @@ class MoELayer:
         self.tracer = NULL_TRACER
         if fused_combine:
             buf.enable_push()
+        # The dispatched rows are an activation that backward needs again, while backward's own
+        # dispatch reuses the Buffer's row shard; by default forward therefore copies them out.
+        # With ``hidden_in_place`` the Buffer gets a second shard for the forward rows and the copy
+        # (NvS x H bf16 read + written) is saved.  Valid as long as this layer's backward runs
+        # before its next forward (no second forward in between, e.g. for recomputation).
+        self.hidden_in_place = hidden_in_place
+        if hidden_in_place:
+            buf.enable_second_shard()
         dev = torch.device("cuda", buf.device)
         H, E, epn = buf.H, buf.E, buf.epn
         g = torch.Generator(device=dev).manual_seed(seed * 7919 + 13)

@@ -98,6 +98,41 @@ def test_fused_sgd_step_is_bit_identical():
     buf.destroy()
 
 
+def test_forward_rows_kept_in_second_shard():
+    """``hidden_in_place`` (forward dispatch lands in a second shard and is used in place) gives
+    the same step as copying the rows out, and ``Buffer.dispatch(shard=1)`` returns the same rows."""
+    from moonep_b200 import Buffer
+    from moonep_b200.models.moe_layer import MoELayer
+    from moonep_b200.ops import gemm
+    S, H, Hp, K, E = 256, 256, 128, 4, 8
+    buf = Buffer(S, H, K, E, 1, num_sms=4, token_padding=64, timeout_s=5.0)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    dy = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    res = []
+    for in_place in (False, True):
+        layer = MoELayer(buf, Hp, None, seed=3, init_std=0.06, hidden_in_place=in_place)
+        for _ in range(2):                       # twice: the shards are reused step after step
+            xo = x.clone().requires_grad_(True)
+            y = layer(xo)
+            y.backward(dy)
+            layer.sgd_step(0.1)
+        torch.cuda.synchronize()
+        buf.check()
+        gemm.check_status()
+        res.append((y.detach().clone(), xo.grad.clone(), layer.w_gate.clone(), layer.w_down.clone()))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    topk = torch.randint(0, E, (S, K), device="cuda", dtype=torch.int32)
+    tpe = torch.bincount(topk.flatten().long(), minlength=E).to(torch.int32)
+    h0, _, _, plan = buf.dispatch(x, None, topk, tpe)
+    h1, _, _, _ = buf.dispatch(x, None, plan=plan, zero_copy=True, shard=1)
+    assert h1.data_ptr() == buf.hidden_view(1).data_ptr() != buf.hidden_view(0).data_ptr()
+    rows = int(plan.cu_seqlens[-1])
+    assert torch.equal(h0[:rows], h1[:rows])
+    buf.destroy()
+
+
 def test_router_topk_kernel():
     from moonep_b200.ops import elementwise as ew
     g = torch.Generator(device="cuda").manual_seed(1)
