@@ -96,3 +96,15 @@ def test_sim_bf16_prologue_rounding_and_dedup_views():
 def test_maxvio_definition():
     tpe = torch.tensor([10, 10, 10, 30])
     assert abs(maxvio(tpe) - 1.0) < 1e-9
+
+
+def test_cpu_benchmark_script_runs(capsys, monkeypatch):
+    """``benchmarks/bench_sim.py`` (configuration 1 on the CPU) exits cleanly and reports ok."""
+    import json
+    import runpy
+    import sys
+    monkeypatch.setattr(sys, "argv", ["bench_sim.py", "--R", "4", "--S", "64", "--E", "16", "--H", "32",
+                                      "--K", "4", "--maxvio", "0,2"])
+    runpy.run_path("benchmarks/bench_sim.py", run_name="__main__")
+    lines = [json.loads(line) for line in capsys.readouterr().out.strip().splitlines()]
+    assert len(lines) == 2 and all(rec["ok"] and rec["rows_per_rank"] == 64 * 4 for rec in lines)
