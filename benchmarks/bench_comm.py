@@ -115,12 +115,13 @@ def main():
         row["k_plan_us"] = timed(lambda: (nat.call(
             "mep_launch_plan", buf._ctx, topk.data_ptr(), tpe.data_ptr(), plan.dst.data_ptr(),
             plan.cu_seqlens.data_ptr(), plan.zero_fill_ranges.data_ptr(), plan.experts_to_copy.data_ptr(),
-            plan.remote_stats.data_ptr(), stream()), nat.call("mep_launch_sync", buf._ctx, stream())))
+            plan.remote_stats.data_ptr(), plan.send_order.data_ptr(), stream()),
+            nat.call("mep_launch_sync", buf._ctx, stream())))
         row["k_dispatch_us"] = timed(lambda: nat.call(
             "mep_launch_dispatch", buf._ctx, x.data_ptr(), 0, plan.dst.data_ptr(),
-            plan.zero_fill_ranges.data_ptr(), 0, 0, 1, 0, stream()))
+            plan.zero_fill_ranges.data_ptr(), 0, 0, 1, 0, 0, stream()))
         row["k_expand_us"] = timed(lambda: nat.call(
-            "mep_launch_expand", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), stream()))
+            "mep_launch_expand", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), 0, stream()))
         row["k_prologue_us"] = timed(lambda: nat.call(
             "mep_launch_combine_prologue", buf._ctx, plan.link.data_ptr(), plan.cu_seqlens.data_ptr(), stream()))
         row["k_combine_us"] = timed(lambda: nat.call(

@@ -41,16 +41,12 @@ def main():
     ap.add_argument("--Hp", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--only", default="")
-    ap.add_argument("--debug-mode", type=int, default=0,
-                    help="kernel timing experiment, a bit mask (results are wrong unless 0 or 16): 1 no "
-                         "epilogue stores, 2 no TMEM loads, 4 no MMAs, 8 no TMA loads, 16 plain-store epilogue")
     ap.add_argument("--ab", action="store_true",
                     help="interleaved A/B of the kernel variants (single CTA / CTA pair, TMA-store / plain "
                          "epilogue, weight grad with and without the fused SGD step): best of 6 rounds each, "
                          "run back to back so that all variants see the same clocks")
     args = ap.parse_args()
     G, rpg, H, Hp = args.groups, args.rows_per_group, args.H, args.Hp
-    gemm.DEBUG_MODE = args.debug_mode
     rows = G * rpg
     dev = "cuda"
     peaks = {}
@@ -116,7 +112,7 @@ def ab(args, ops, x, act, cu, grad, w, out):
         torch.cuda.synchronize()
         return a.elapsed_time(b) / n
 
-    variants = [("single", 0, 0), ("single_plain_epilogue", 0, 16), ("pair", 1, 0), ("pair_plain_epilogue", 1, 16)]
+    variants = [("single", 0, False), ("single_plain_epilogue", 0, True), ("pair", 1, False), ("pair_plain_epilogue", 1, True)]
     ops = dict(ops)
     ops.pop("cublas_ref_down(torch.bmm)", None)
     flops_w = ops["wgrad"][1]
@@ -124,18 +120,18 @@ def ab(args, ops, x, act, cu, grad, w, out):
     for name, (fn, flops) in ops.items():
         if args.only and args.only not in name:
             continue
-        vs = [v for v in variants if "wgrad" not in name or v[2] == 0]
+        vs = [v for v in variants if "wgrad" not in name or not v[2]]
         for _, two, dbg in vs:
-            gemm.TWO_CTA, gemm.DEBUG_MODE = two, dbg | args.debug_mode
+            gemm.TWO_CTA, gemm.PLAIN_EPILOGUE = two, dbg
             fn()
         torch.cuda.synchronize()
         best = {v[0]: 1e9 for v in vs}
         for _ in range(6):
             for v, two, dbg in vs:
-                gemm.TWO_CTA, gemm.DEBUG_MODE = two, dbg | args.debug_mode
+                gemm.TWO_CTA, gemm.PLAIN_EPILOGUE = two, dbg
                 best[v] = min(best[v], run(fn))
         out[name] = {v: {"ms": round(t, 4), "tflops": round(flops / t / 1e9)} for v, t in best.items()}
-    gemm.TWO_CTA, gemm.DEBUG_MODE = 2, 0
+    gemm.TWO_CTA, gemm.PLAIN_EPILOGUE = 2, False
     gemm.check_status()
     print(json.dumps(out))
 

@@ -42,11 +42,13 @@ nat.declare("mep_sync_state_ints", I, [])
 nat.declare("mep_meta_offsets", None, [L, I, I, ctypes.POINTER(ctypes.c_int64)])
 nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
 nat.declare("mep_ctx_destroy", None, [P])
-nat.declare("mep_ctx_set_hidden", I, [P, P, L])
-nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P])
-nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, P, I, I, P])
+nat.declare("mep_ctx_set_second_shard", I, [P, P])
+nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P, P])
+nat.declare("mep_launch_arrive_reset", I, [P, P])
+nat.declare("mep_launch_plan_snapshot", I, [P, P, P, P])
+nat.declare("mep_launch_dispatch", I, [P, P, P, P, P, P, P, I, I, I, P])
 nat.declare("mep_launch_push_reduce", I, [P, P, L, P, L, P, P, P, P, P, I, P])
-nat.declare("mep_launch_expand", I, [P, P, P, P])
+nat.declare("mep_launch_expand", I, [P, P, P, I, P])
 nat.declare("mep_launch_combine_prologue", I, [P, P, P, P])
 nat.declare("mep_launch_combine", I, [P, P, P, P, P])
 nat.declare("mep_launch_prefetch", I, [P, P, I, P, P, P, P, P])
@@ -224,17 +226,28 @@ class Buffer:
             self.hidden_buf2 = symm.create_nvl_dist_tensor((self.NvS, self.H), torch.bfloat16, group=self.group,
                                                            device=self.device)
         assert self.hidden_buf2.shape[0] // self.R == self.hidden_stride
+        self._rc(nat.call("mep_ctx_set_second_shard", self._ctx, self.hidden_buf2.data_ptr()), "second shard")
+
+    def claim_second_shard(self, owner) -> None:
+        """Marks the second shard as holding ``owner``'s rows.  A claim by anyone else before
+        ``release_second_shard`` raises: the Buffer has one second shard, and a ``shard=1``
+        dispatch of another user would silently overwrite rows that are still needed."""
+        cur = getattr(self, "_shard1_owner", None)
+        if cur is not None and cur is not owner:
+            raise RuntimeError(
+                "the Buffer's second shard still holds rows that another layer keeps for its backward "
+                "pass; give every layer that uses hidden_in_place its own Buffer, or switch the flag off")
+        self._shard1_owner = owner
+
+    def release_second_shard(self, owner) -> None:
+        if getattr(self, "_shard1_owner", None) is owner:
+            self._shard1_owner = None
 
     def hidden_view(self, shard: int = 0) -> torch.Tensor:
         """``hidden_nvsh_buffer_view`` of the given shard."""
         self._require()
         v = self._shards(shard)
         return v if self.virtual else v[0]
-
-    def _select_shard(self, shard: int) -> None:
-        buf = self.hidden_buf if shard == 0 else self.hidden_buf2
-        assert shard in (0, 1) and buf is not None, "shard must be 0, or 1 after enable_second_shard()"
-        self._rc(nat.call("mep_ctx_set_hidden", self._ctx, buf.data_ptr(), self.hidden_stride), "select shard")
 
     def _meta_rows(self) -> torch.Tensor:
         mb = self.meta_buf.view(self.R, self.meta_stride)
@@ -344,18 +357,13 @@ class Buffer:
             assert plan.N == self.N and plan.NvS == self.NvS and plan.R == self.R, \
                 "plan was made by a Buffer of another shape"
 
+        assert shard == 0 or (shard == 1 and self.hidden_buf2 is not None), \
+            "shard must be 0, or 1 after enable_second_shard()"
+
         def run():
-            if shard == 0:
-                return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
-                                                        tokens_per_expert, plan, inter_rank_sync,
-                                                        zero_copy, router_weights_zero_copy)
-            self._select_shard(shard)
-            try:
-                return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
-                                                        tokens_per_expert, plan, inter_rank_sync,
-                                                        zero_copy, router_weights_zero_copy, shard)
-            finally:
-                self._select_shard(0)
+            return self._dispatch_on_current_stream(hidden_sh, route_weights_sk, topk_experts_sk,
+                                                    tokens_per_expert, plan, inter_rank_sync,
+                                                    zero_copy, router_weights_zero_copy, shard)
 
         if async_finish:
             out, ev = self._run_async([hidden_sh, route_weights_sk, topk_experts_sk, tokens_per_expert], run)
@@ -372,27 +380,14 @@ class Buffer:
         fresh = plan is None
         i32 = dict(dtype=torch.int32, device=dev)
         if fresh:
-            dst = torch.empty(self._shape(self.N), **i32)
-            cu = torch.empty(self._shape(2 * self.epn), **i32)
-            zf = torch.empty(self._shape(2 * self.epn, 2), **i32)
-            etc = torch.empty(self._shape(self.R, self.epn), **i32)
-            rs = torch.empty(self._shape(2), **i32)
-            link = torch.empty(self._shape(self.NvS), **i32)
-            src = torch.empty(self._shape(self.NvS), **i32)
-            self._rc(nat.call("mep_launch_plan", self._ctx, topk.data_ptr(), tpe.data_ptr(),
-                              dst.data_ptr(), cu.data_ptr(), zf.data_ptr(), etc.data_ptr(),
-                              rs.data_ptr(), st), "plan")
-            plan = CommPlan(dst=dst, experts_to_copy=etc, zero_fill_ranges=zf, remote_stats=rs,
-                            cu_seqlens=cu, link=link, N=self.N, R=self.R, E=self.E, NvS=self.NvS,
-                            K=self.K, src_info=src)
-            self._last_plan = plan
+            plan = self._fresh_plan(topk, tpe, dev, st)
         self._rc(nat.call("mep_launch_dispatch", self._ctx, x.data_ptr(), nat.ptr(w),
                           plan.dst.data_ptr(), plan.zero_fill_ranges.data_ptr(),
                           plan.link.data_ptr() if fresh else 0,
                           plan.src_info.data_ptr() if fresh else 0,
-                          int(bool(inter_rank_sync) and not fresh), int(fresh), st), "dispatch")
+                          int(bool(inter_rank_sync) and not fresh), int(fresh), shard, st), "dispatch")
         self._rc(nat.call("mep_launch_expand", self._ctx, plan.link.data_ptr(),
-                          plan.cu_seqlens.data_ptr(), st), "dispatch expand")
+                          plan.cu_seqlens.data_ptr(), shard, st), "dispatch expand")
         view = self.hidden_view(shard)
         hidden = view if zero_copy else view.clone()
         weights = None
@@ -403,6 +398,89 @@ class Buffer:
         self._stats["bytes_dispatch"] += self.N * self.H * 2 * self.Rv
         self._maybe_check()
         return hidden, weights, (plan.cu_seqlens if fresh else None), plan
+
+    def _fresh_plan(self, topk, tpe, dev, st) -> CommPlan:
+        i32 = dict(dtype=torch.int32, device=dev)
+        dst = torch.empty(self._shape(self.N), **i32)
+        cu = torch.empty(self._shape(2 * self.epn), **i32)
+        zf = torch.empty(self._shape(2 * self.epn, 2), **i32)
+        etc = torch.empty(self._shape(self.R, self.epn), **i32)
+        rs = torch.empty(self._shape(2), **i32)
+        link = torch.empty(self._shape(self.NvS), **i32)
+        src = torch.empty(self._shape(self.NvS), **i32)
+        order = torch.empty(self._shape(self.N), **i32)
+        self._rc(nat.call("mep_launch_plan", self._ctx, topk.data_ptr(), tpe.data_ptr(),
+                          dst.data_ptr(), cu.data_ptr(), zf.data_ptr(), etc.data_ptr(),
+                          rs.data_ptr(), order.data_ptr(), st), "plan")
+        plan = CommPlan(dst=dst, experts_to_copy=etc, zero_fill_ranges=zf, remote_stats=rs,
+                        cu_seqlens=cu, link=link, N=self.N, R=self.R, E=self.E, NvS=self.NvS,
+                        K=self.K, src_info=src, send_order=order)
+        self._last_plan = plan
+        return plan
+
+    # ---- dispatch fused into the consuming GEMM ---------------------------------------------
+    def fused_dispatch_supported(self) -> bool:
+        """The fused dispatch -> GEMM path needs tiles that never straddle two groups
+        (``token_padding % 128 == 0``), rows that split into equal 16-byte multiples of at most
+        7 KB, and one rank per process."""
+        row = self.H * 2
+        nsplit = (row + 7167) // 7168
+        return (not self.virtual) and self.token_padding % 128 == 0 and row % (16 * nsplit) == 0
+
+    def dispatch_fused_begin(self, hidden_sh, route_weights_sk=None, topk_experts_sk=None,
+                             tokens_per_expert=None, plan: Optional[CommPlan] = None, *, shard: int = 0):
+        """First half of a dispatch whose all-to-all runs INSIDE the grouped GEMM that consumes
+        the rows (``ops.gemm.gateup_swiglu`` / ``down_dgrad`` with ``dispatch=``): nothing is sent
+        here.  A fresh plan is made (or, with ``plan``, the group meets and the arrival counters
+        are cleared) and the arguments of the fused launches are returned.
+
+        Returns ``(hidden_nvsh_view, route_weights_view | None, cu_seqlens | None, plan, disp)``.
+        The two views alias the Buffer's row buffer ``shard`` and its weight slots; they hold the
+        dispatched data only once the GEMM launches that were given ``disp`` (the first one) or
+        ``dict(disp, mode=1)`` (any further one over the same rows) have run.  Finish with
+        ``dispatch_fused_end``.  The reference has no counterpart: its dispatch ends with a
+        barrier before the host framework's GEMM may start (moonep/dispatch.py:687-691)."""
+        self._require()
+        assert self.fused_dispatch_supported(), "this Buffer's shape cannot use the fused dispatch"
+        assert hidden_sh.dtype == torch.bfloat16 and hidden_sh.is_cuda and hidden_sh.is_contiguous()
+        assert tuple(hidden_sh.shape) == (self.S, self.H) and hidden_sh.data_ptr() % 16 == 0
+        assert shard == 0 or (shard == 1 and self.hidden_buf2 is not None), \
+            "shard must be 0, or 1 after enable_second_shard()"
+        if route_weights_sk is not None:
+            assert route_weights_sk.dtype == torch.float32 and route_weights_sk.is_contiguous()
+            assert tuple(route_weights_sk.shape) == (self.S, self.K)
+        st = self._stream()
+        fresh = plan is None
+        if fresh:
+            assert topk_experts_sk is not None and tokens_per_expert is not None, \
+                "topk_experts_sk and tokens_per_expert are required for a fresh plan"
+            assert topk_experts_sk.dtype == torch.int32 and topk_experts_sk.is_contiguous()
+            assert tokens_per_expert.dtype == torch.int32 and tokens_per_expert.is_contiguous()
+            plan = self._fresh_plan(topk_experts_sk, tokens_per_expert, hidden_sh.device, st)
+        else:
+            assert plan.N == self.N and plan.NvS == self.NvS and plan.R == self.R
+            assert plan.send_order is not None, "plan has no sending order"
+            self._rc(nat.call("mep_launch_arrive_reset", self._ctx, st), "dispatch (fused) entry")
+        disp = dict(mode=2, ctx=self._ctx, x=hidden_sh, w=route_weights_sk, dst=plan.dst,
+                    order=plan.send_order, zero_fill=plan.zero_fill_ranges, fresh=int(fresh), shard=shard)
+        self._stats["dispatch"] += 1
+        self._stats["bytes_dispatch"] += self.N * self.H * 2
+        wv = self.router_weight_buffer_view if route_weights_sk is not None else None
+        return self.hidden_view(shard), wv, (plan.cu_seqlens if fresh else None), plan, disp
+
+    def dispatch_fused_end(self, plan: CommPlan, disp: dict, clone_weights: bool = True):
+        """Second half: call after the GEMM launches that carried ``disp``.  For a fresh plan the
+        plan's chain links and source records are copied out of the meta chunk.  Returns the
+        dispatched route weights ``[NvS]`` (a copy unless ``clone_weights=False``) or ``None``."""
+        self._require()
+        if disp["fresh"]:
+            self._rc(nat.call("mep_launch_plan_snapshot", self._ctx, plan.link.data_ptr(),
+                              plan.src_info.data_ptr(), self._stream()), "plan snapshot")
+        self._maybe_check()
+        if disp["w"] is None:
+            return None
+        wv = self.router_weight_buffer_view
+        return wv.clone() if clone_weights else wv
 
     # ---- combine ----------------------------------------------------------------------------
     def combine(self, plan: Optional[CommPlan] = None, hidden_nvsh=None, route_weights_nvs=None,

@@ -202,6 +202,42 @@ __global__ void __launch_bounds__(EXPAND_THREADS) ep_expand_kernel(const ExpandP
   }
 }
 
+// ---- fused dispatch -> GEMM path: the two small kernels around the fused GEMM launches ----------
+// (the dispatch itself runs inside the GEMM kernel, device/fused_dispatch.cuh)
+struct ArriveResetParams {
+  SyncCtx sync;
+  int64_t arrive_off;
+  int n_arrive;
+};
+// Dispatch with a saved plan: clear this rank's arrival counters, then meet the group.  The
+// barrier does what the entry barrier of the stand-alone dispatch does (every peer has finished
+// reading this rank's row buffer) and orders the clear before every peer's first increment.
+// With a fresh plan the planner kernel does both.
+__global__ void __launch_bounds__(128, 1) ep_arrive_reset_kernel(const ArriveResetParams p) {
+  const SyncCtx& sc = p.sync;
+  const int rank = sc.rank_base + (int)blockIdx.y;
+  int32_t* arrive = sc.meta + (size_t)rank * sc.meta_stride + p.arrive_off;
+  for (int i = threadIdx.x; i < p.n_arrive; i += blockDim.x) arrive[i] = 0;
+  cta_cross_rank_exchange(sc, 1);
+}
+
+struct SnapshotParams {
+  const int32_t* link_src;
+  const int32_t* src_src;
+  int32_t* link_out;
+  int32_t* src_out;
+  int64_t n;
+};
+// Copies this rank's chain links and source records out of the meta chunk into the plan, once
+// the fused GEMM launches of a fresh plan have completed (every block of rows has then arrived,
+// and a source publishes its records before it sends its first row).
+__global__ void __launch_bounds__(256) ep_plan_snapshot_kernel(const SnapshotParams p) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.n; i += (int64_t)gridDim.x * blockDim.x) {
+    p.link_out[i] = p.link_src[i];
+    p.src_out[i] = p.src_src[i];
+  }
+}
+
 template <int ST>
 static int launch_dispatch_t(const BufferCtx& c, DispatchParams& p, size_t smem,
                              cudaStream_t stream) {
@@ -225,19 +261,21 @@ extern "C" {
 
 // x [Rv][S][H] bf16, w [Rv][S][K] fp32 or null, dst [Rv][N], zero_fill [Rv][2epn][2],
 // link_out [Rv][NvS] or null.  fresh != 0: the plan comes from the planner launch that
-// precedes this one on the stream (its barrier stands in for the entry sync).
+// precedes this one on the stream (its barrier stands in for the entry sync).  shard selects
+// the row buffer the rows land in (0, or 1 once a second shard is registered).
 int mep_launch_dispatch(const void* ctx_, const void* x, const float* w, const int32_t* dst,
                         const int32_t* zero_fill, int32_t* link_out, int32_t* src_out, int entry_barrier,
-                        int fresh, cudaStream_t stream) {
+                        int fresh, int shard, cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (c.H % 8 != 0) return fail(-1, "dispatch needs H %% 8 == 0 (got %d)", c.H);
+  if (c.shard_base(shard) == nullptr) return fail(-4, "dispatch: shard %d does not exist", shard);
   DispatchParams p;
   p.sync = c.sync(KID_DISPATCH);
   p.S = c.S; p.K = c.K; p.H = c.H; p.epn = c.epn;
   p.N = c.N; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
   p.weights_off = c.ml.weights_off; p.link_off = c.ml.link_off; p.src_off = c.ml.src_off;
   p.x = (const __nv_bfloat16*)x; p.w = w; p.dst = dst; p.zero_fill = zero_fill;
-  p.hidden = (__nv_bfloat16*)c.hidden; p.link_out = link_out; p.src_out = src_out;
+  p.hidden = (__nv_bfloat16*)c.shard_base(shard); p.link_out = link_out; p.src_out = src_out;
   p.entry_barrier = entry_barrier; p.fresh = fresh;
   const size_t row = (size_t)c.H * 2;
   // virtual groups must keep gridDim.x * R CTAs co-resident: leave room for 2 CTAs per SM
@@ -249,16 +287,42 @@ int mep_launch_dispatch(const void* ctx_, const void* x, const float* w, const i
 }
 
 // Copy every primary row to its duplicates inside this rank's shard.
-int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_seqlens,
+int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_seqlens, int shard,
                       cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
+  if (c.shard_base(shard) == nullptr) return fail(-4, "expand: shard %d does not exist", shard);
   ExpandParams p;
   p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
   p.rank_base = c.virt ? 0 : c.rank;
-  p.hidden = (__nv_bfloat16*)c.hidden; p.link = link; p.cu_seqlens = cu_seqlens;
+  p.hidden = (__nv_bfloat16*)c.shard_base(shard); p.link = link; p.cu_seqlens = cu_seqlens;
   // latency-bound row walks: several CTAs per SM keep enough loads in flight
   dim3 grid(c.num_sms_local * 6, c.Rv());
   ep_expand_kernel<<<grid, EXPAND_THREADS, 0, stream>>>(p);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Saved-plan entry of the fused dispatch -> GEMM path (see ep_arrive_reset_kernel).
+int mep_launch_arrive_reset(const void* ctx_, cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  ArriveResetParams p;
+  p.sync = c.sync(KID_DISPATCH);
+  p.arrive_off = c.ml.arrive_off;
+  p.n_arrive = (int)(c.NvS / 128 + 1);
+  dim3 grid(1, c.Rv());
+  MEP_CUDA_OK(launch_coop((const void*)ep_arrive_reset_kernel, grid, dim3(128), 0, stream, p));
+  return 0;
+}
+
+// Fresh-plan exit of the fused path: link_out / src_out [NvS] of the plan.
+int mep_launch_plan_snapshot(const void* ctx_, int32_t* link_out, int32_t* src_out, cudaStream_t stream) {
+  const BufferCtx& c = *(const BufferCtx*)ctx_;
+  if (c.virt) return fail(-1, "plan snapshot: the fused path runs one rank per launch");
+  SnapshotParams p;
+  const int32_t* mine = c.meta + (size_t)c.rank * c.meta_stride;
+  p.link_src = mine + c.ml.link_off; p.src_src = mine + c.ml.src_off;
+  p.link_out = link_out; p.src_out = src_out; p.n = c.NvS;
+  ep_plan_snapshot_kernel<<<32, 256, 0, stream>>>(p);
   MEP_CUDA_OK(cudaGetLastError());
   return 0;
 }

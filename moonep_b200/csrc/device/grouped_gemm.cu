@@ -37,6 +37,10 @@
 // cover 256 rows of one group; weight-grad pairs 256 rows of the weight matrix.
 // Measured A/B (32 groups x 1024 rows, H=7168, H'=2048, interleaved runs under the power cap):
 // pairs +13% gate/up, +13% down, +18% down dgrad, +7% gate/up dgrad, +24% weight grad.
+// Fused dispatch (template DISP, token-major kernels whose A operand is the dispatched rows): a
+// seventh warp per CTA sends this rank's token rows to their destination ranks while the other
+// warps compute, and the TMA producer waits for a tile's rows to have arrived before it loads
+// them (device/fused_dispatch.cuh).  That variant gives up one operand stage for the copy ring.
 // Every mbarrier wait is bounded; on expiry the CTA records an error, drains and frees TMEM.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -44,7 +48,9 @@
 
 #include <cstring>
 
+#include "device/fused_dispatch.cuh"
 #include "device/tcgen05.cuh"
+#include "host/ctx.h"
 #include "host/errors.h"
 
 namespace mep {
@@ -55,6 +61,7 @@ constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS_DISP = 224;      // + the copy warp of the fused dispatch
 constexpr int MAX_GROUPS = 1024;
 // CTA-pair variant: each CTA stages A (16 KB) and half of B (16 KB) per k-block, six stages.
 constexpr int GEMM_STAGES2 = 6;
@@ -70,9 +77,11 @@ struct GemmKParams {
   CUtensorMap o;           // bf16 output of the token-major epilogue (32 x 64 store boxes)
   const int32_t* cu_seqlens;
   int ngroups, split, total_rows, N, K, nseg, rows_per_expert, Mw, accumulate, zero_empty_below;
-  // timing experiments only (results are wrong when non-zero), a bit mask: 1 = skip the epilogue's
-  // global stores, 2 = skip its TMEM loads, 4 = issue no MMAs (barriers only), 8 = issue no TMA
-  // loads (barriers only), 16 = plain-store epilogues (results stay correct)
+  // Timing experiments, compiled in only with -DMEP_GEMM_EXPERIMENTS (results are wrong when
+  // non-zero), a bit mask: 1 = skip the epilogue's global stores, 2 = skip its TMEM loads, 4 =
+  // issue no MMAs (barriers only), 8 = issue no TMA loads (barriers only).  In a normal build
+  // gemm_dbg() is a constant false and none of those branches exists.  Bit 16 (plain-store
+  // epilogues, results stay correct) is a host-side choice of the epilogue and always available.
   int debug;
   int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
   int tma_out; // outputs are 16-byte aligned: whole 32-row blocks leave through TMA stores
@@ -94,7 +103,14 @@ struct GemmKParams {
   void* push_base;
   long long push_rank_stride;
   int push_entries, push_ranks;
+  FusedDispatch disp;      // DISP kernels only
 };
+
+#ifdef MEP_GEMM_EXPERIMENTS
+__device__ __forceinline__ bool gemm_dbg(const GemmKParams& p, int bit) { return (p.debug & bit) != 0; }
+#else
+__device__ __forceinline__ constexpr bool gemm_dbg(const GemmKParams&, int) { return false; }
+#endif
 
 struct Tile {
   int g, row0, rows, n0, num_kb, alloc, g_local, m0;
@@ -119,6 +135,33 @@ __device__ __forceinline__ bool gemm_wait(uint64_t* bar, uint32_t parity, volati
           p.status[1] = KID_GEMM;
           p.status[2] = where;
           p.status[3] = (int)blockIdx.x;
+        }
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// Fused dispatch: wait until all rows of the 128-row block have arrived (counter >= expect).
+__device__ __forceinline__ bool arrive_wait(const int32_t* ctr, int expect, int block, volatile int* s_abort,
+                                            const GemmKParams& p) {
+  int seen = ld_acquire_sys(ctr);
+  if (seen >= expect) return true;
+  unsigned long long t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while ((seen = ld_acquire_sys(ctr)) < expect) {
+    if ((++spins & 63u) == 0) {
+      if (*s_abort) return false;
+      if (globaltimer_ns() - t0 > p.timeout_ns) {
+        *s_abort = 1;
+        if (p.status != nullptr && atomicCAS(p.status, 0, ST_TIMEOUT_ARRIVAL) == 0) {
+          p.status[1] = KID_GEMM;
+          p.status[2] = 6;
+          p.status[3] = (int)blockIdx.x;
+          p.status[4] = block;
+          p.status[5] = seen;
+          p.status[6] = expect;
         }
         return false;
       }
@@ -178,18 +221,25 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
 
 // SGD (weight grad only): the optimizer step is fused into the epilogue.  That variant gives up
 // one stage of the operand ring for a ring of weight blocks per epilogue warp (see the epilogue).
-template <bool TWO, bool SGD> __host__ __device__ constexpr int gemm_stages() { return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (SGD ? 1 : 0); }
+template <bool TWO, bool SGD, bool DISP = false> __host__ __device__ constexpr int gemm_stages() {
+  return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (SGD ? 1 : 0) - (DISP ? 1 : 0);
+}
 template <bool TWO> __host__ __device__ constexpr int sgd_ring() { return TWO ? 2 : 3; }   // 4 KB weight blocks per warp
-template <bool TWO, bool SGD> __host__ __device__ constexpr int gemm_smem() {   // dynamic shared memory
-  return gemm_stages<TWO, SGD>() * (TWO ? STAGE_BYTES2 : STAGE_BYTES) + 1024 +
-         (SGD ? 4 * sgd_ring<TWO>() * 4096 : 0);
+// Fused dispatch: stages of the copy ring (the pair kernel with the staged bf16 epilogue has less
+// shared memory to spare).
+template <bool TWO, int EPI> __host__ __device__ constexpr int fd_stages() { return (TWO && EPI == EPI_BF16) ? 5 : 8; }
+template <bool TWO, bool SGD, bool DISP = false, int EPI = EPI_BF16> __host__ __device__ constexpr int gemm_smem() {   // dynamic shared memory
+  return gemm_stages<TWO, SGD, DISP>() * (TWO ? STAGE_BYTES2 : STAGE_BYTES) + 1024 +
+         (SGD ? 4 * sgd_ring<TWO>() * 4096 : 0) + (DISP ? fd_stages<TWO, EPI>() * FD_PART_CAP : 0);
 }
 
-template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false, bool SGD = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false, bool SGD = false, bool DISP = false>
+__global__ void __launch_bounds__(DISP ? GEMM_THREADS_DISP : GEMM_THREADS, 1)
 ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   static_assert(!SGD || (WGRAD && EPI == EPI_F32), "the fused SGD step belongs to the weight grad");
-  constexpr int GEMM_STAGES = gemm_stages<TWO, SGD>();
+  static_assert(!DISP || (!WGRAD && !SGD), "the fused dispatch feeds a token-major GEMM");
+  constexpr int GEMM_STAGES = gemm_stages<TWO, SGD, DISP>();
+  constexpr int FD_NST = fd_stages<TWO, EPI>();
   constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
   constexpr int WB = SGD ? sgd_ring<TWO>() : 1;
   const int crank = TWO ? (int)cluster_cta_rank() : 0;        // 0 = leader of the pair
@@ -213,6 +263,9 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
   // staging of the bf16 epilogue: per warp one 32 x 64 block (128-byte rows, 128B swizzle)
   __shared__ __align__(1024) uint8_t s_out[(!WGRAD && EPI == EPI_BF16) ? 4 * 4096 : 16];
+  // fused dispatch: "landed" barriers of the copy ring, and per stage the destination / counter
+  __shared__ __align__(8) uint64_t fd_full[DISP ? FD_NST : 1];
+  __shared__ unsigned long long fd_slots[DISP ? 2 * FD_NST : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -224,11 +277,12 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
     for (int a = 0; a < 4 * WB; ++a) mbar_init(&wbar[a / WB][a % WB], 1);
+    if constexpr (DISP) for (int a = 0; a < FD_NST; ++a) mbar_init(&fd_full[a], 1);
     mbar_fence_init();
     s_abort = 0;
   }
   // group table
-  for (int g = tid; g < p.ngroups; g += GEMM_THREADS)
+  for (int g = tid; g < p.ngroups; g += (int)blockDim.x)
     s_end[g] = p.cu_seqlens != nullptr ? p.cu_seqlens[g] : p.total_rows;
   __syncthreads();
   if (warp == 0) {
@@ -278,6 +332,13 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
         if (!t.valid) continue;
         const int kb_per_seg = WGRAD ? t.num_kb : (p.K + BK - 1) / BK;
+        if constexpr (DISP) {
+          // the rows of this tile come from other ranks' copy warps: wait until all have landed
+          if (p.disp.arrive != nullptr && t.rows > 0) {
+            if (!arrive_wait(p.disp.arrive + (t.row0 >> 7), p.disp.expect, t.row0 >> 7, abortp, p)) break;
+            fence_proxy_async();   // the rows were written through the async proxy (or by plain stores)
+          }
+        }
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % GEMM_STAGES;
           if (it >= GEMM_STAGES &&
@@ -289,7 +350,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           uint8_t* sb = sa + A_TILE_BYTES;
           uint32_t lead_bar = 0;
           if constexpr (TWO) lead_bar = mapa_u32(&full[s], 0);
-          if (p.debug & 8) {
+          if (gemm_dbg(p, 8)) {
             if (crank == 0) mbar_arrive(&full[s]);
             continue;
           }
@@ -372,7 +433,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           const uint32_t sb = sa + A_TILE_BYTES;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            if (p.debug & 4) break;
+            if (gemm_dbg(p, 4)) break;
             const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
@@ -388,6 +449,16 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         if constexpr (TWO) umma_commit_2cta(&acc_full[acc], 3);   // accumulator complete, both halves
         else umma_commit(&acc_full[acc]);
         ++tile_n;
+      }
+    }
+  } else if (DISP && warp >= 6) {
+    // ================= fused dispatch: this CTA's share of the all-to-all =================
+    if constexpr (DISP) {
+      if (p.disp.x != nullptr) {
+        uint8_t* ring = tiles + (size_t)GEMM_STAGES * STAGE_BYTES;
+        fused_dispatch_copy_warp<FD_NST>(
+            p.disp, ring, fd_full, fd_slots, (int)blockIdx.x, (int)gridDim.x,
+            [&](uint64_t* bar, uint32_t parity) { return gemm_wait(bar, parity, abortp, p, 7); });
       }
     }
   } else {
@@ -450,14 +521,15 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       if constexpr (EPI == EPI_SWIGLU) {
         const bool row_ok = r_in_tile < t.rows;
         const long long row = (long long)t.row0 + r_in_tile;
-        const float rs = (row_ok && p.row_scale != nullptr) ? p.row_scale[row] : 1.f;
+        // (read past L1: with the fused dispatch the scale was written by another rank moments ago)
+        const float rs = (row_ok && p.row_scale != nullptr) ? __ldcg(p.row_scale + row) : 1.f;
         __nv_bfloat16* og = (__nv_bfloat16*)p.out[0];
         __nv_bfloat16* ou = (__nv_bfloat16*)p.out[1];
         __nv_bfloat16* oa = (__nv_bfloat16*)p.out[2];
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t rg[32], ru[32];
-          if (!(p.debug & 2)) {
+          if (!gemm_dbg(p, 2)) {
             tmem_ld_32x32(tacc + c * 32, rg);
             tmem_ld_32x32(tacc + 128 + c * 32, ru);
             tmem_ld_wait();
@@ -485,7 +557,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               pa[i] = *reinterpret_cast<uint32_t*>(&ha);
             }
             const long long off = row * p.ldc + col;
-            if (p.debug & 1) {
+            if (gemm_dbg(p, 1)) {
             } else if (col + 32 <= p.N) {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -589,16 +661,16 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               const int b = wseq % WB;
               uint8_t* wbuf = wring + b * WBLK;
               uint32_t ra[32], rb[32];
-              if (!(p.debug & 2)) {
+              if (!gemm_dbg(p, 2)) {
                 tmem_ld_32x32(tacc + c * WCOLS, ra);
                 tmem_ld_32x32(tacc + c * WCOLS + 32, rb);
               }
               if (!gemm_wait(&wbar[q][b], (uint32_t)(wseq / WB) & 1u, abortp, p, 5)) {
-                if (!(p.debug & 2)) tmem_ld_wait();
+                if (!gemm_dbg(p, 2)) tmem_ld_wait();
                 wok = false;
                 break;
               }
-              if (!(p.debug & 2)) {
+              if (!gemm_dbg(p, 2)) {
                 tmem_ld_wait();
               } else {
 #pragma unroll
@@ -621,7 +693,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
-                if (!(p.debug & 1)) {
+                if (!gemm_dbg(p, 1)) {
                   tma_store_2d(&p.wmap, col_base + c * WCOLS, y0, wbuf);
                   bulk_commit();
                 }
@@ -635,7 +707,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
-            if (have_acc && !(p.debug & 2)) {
+            if (have_acc && !gemm_dbg(p, 2)) {
               tmem_ld_32x32(tacc + c * 32, r);
               tmem_ld_wait();
             } else {
@@ -651,7 +723,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             fence_proxy_async_smem();
             __syncwarp();
             const int x0 = col_base + c * 32;
-            if (lane == 0 && x0 < p.N && !(p.debug & 1)) {
+            if (lane == 0 && x0 < p.N && !gemm_dbg(p, 1)) {
               if (p.accumulate) tma_reduce_add_2d(cmap, x0, y0, pad);
               else tma_store_2d(cmap, x0, y0, pad);
               bulk_commit();
@@ -669,7 +741,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
-            if (have_acc && !(p.debug & 2)) {
+            if (have_acc && !gemm_dbg(p, 2)) {
               tmem_ld_32x32(tacc + c * 32, r);
               tmem_ld_wait();
             } else {
@@ -680,7 +752,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) pad[lane * 33 + i] = __uint_as_float(r[i]);
             __syncwarp();
-            if (col < p.N && !(p.debug & 1)) {
+            if (col < p.N && !gemm_dbg(p, 1)) {
               float* o = (float*)outp + off_warp + col;
 #pragma unroll 8
               for (int rr = 0; rr < 32; ++rr) {
@@ -703,7 +775,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             const int col = col_base + c2 * 64;
             if (col >= p.N) break;
             uint32_t ra[32], rb[32];
-            if (have_acc && !(p.debug & 2)) {
+            if (have_acc && !gemm_dbg(p, 2)) {
               tmem_ld_32x32(tacc + c2 * 64, ra);
               tmem_ld_32x32(tacc + c2 * 64 + 32, rb);
               tmem_ld_wait();
@@ -727,7 +799,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0 && !(p.debug & 1)) {
+            if (lane == 0 && !gemm_dbg(p, 1)) {
               tma_store_2d(&p.o, col, y0, pad);
               bulk_commit();
             }
@@ -736,7 +808,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
-          if (have_acc && !(p.debug & 2)) {
+          if (have_acc && !gemm_dbg(p, 2)) {
             tmem_ld_32x32(tacc + c * 32, r);
             tmem_ld_wait();
           } else {
@@ -744,7 +816,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
           const int col = col_base + c * 32;
-          if (!row_ok || col >= p.N || (p.debug & 1)) continue;
+          if (!row_ok || col >= p.N || gemm_dbg(p, 1)) continue;
           if constexpr (EPI == EPI_F32) {
             // unreachable: the fp32 epilogue is the transposed loop below
           } else {
@@ -816,7 +888,17 @@ struct GemmDesc {
   void* sgd_w;
   const int32_t* sgd_keep;
   float sgd_lr;
-  int32_t pad3_;
+  // Fused dispatch (0 = off): 1 = only wait for the rows of each tile to arrive, 2 = also send
+  // this rank's rows.  disp_ctx is the Buffer's context; the A operand must be the row buffer
+  // `disp_shard` of that Buffer.
+  int32_t disp_mode;
+  const void* disp_ctx;
+  const void* disp_x;
+  const float* disp_w;
+  const int32_t* disp_dst;
+  const int32_t* disp_order;
+  const int32_t* disp_zero_fill;
+  int32_t disp_fresh, disp_shard;
 };
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -860,10 +942,10 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
 }
 
 // CTA-pair launch: clusters of two CTAs, one pair per two SMs.
-template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false>
+template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false, bool DISP = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
-  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true, SGD>;
-  constexpr int GEMM_SMEM2 = gemm_smem<true, SGD>();
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true, SGD, DISP>;
+  constexpr int GEMM_SMEM2 = gemm_smem<true, SGD, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
     MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM2));
@@ -872,14 +954,18 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)(grid / 2 * 2));
-  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.blockDim = dim3(DISP ? GEMM_THREADS_DISP : GEMM_THREADS);
   cfg.dynamicSmemBytes = GEMM_SMEM2;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  // the fused dispatch makes CTAs of different ranks wait for one another's copy warps: the
+  // whole grid must be resident at once, which a cooperative launch guarantees
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = DISP ? 2 : 1;
   // A persistent grid must not exceed what is resident at once: not every SM can be paired
   // into a cluster (GPCs with an odd SM count leave one out), and a second wave of persistent
   // CTAs would double the run time.
@@ -907,14 +993,24 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   return 0;
 }
 
-template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool SGD = false>
+template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool SGD = false, bool DISP = false>
 static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
-  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, false, SGD>;
-  constexpr int GEMM_SMEM = gemm_smem<false, SGD>();
+  auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, false, SGD, DISP>;
+  constexpr int GEMM_SMEM = gemm_smem<false, SGD, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
     MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
     configured = true;
+  }
+  if constexpr (DISP) {
+    // CTAs of different ranks wait for one another's copy warps: all of them must be resident
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (grid > sms) grid = sms;
+    GemmKParams kpc = kp;
+    MEP_CUDA_OK(launch_coop((const void*)kern, dim3(grid), dim3(GEMM_THREADS_DISP), GEMM_SMEM, stream, kpc));
+    return 0;
   }
   kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(kp);
   MEP_CUDA_OK(cudaGetLastError());
@@ -1005,6 +1101,46 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
     kp.tma_out = (d->debug & 16) ? 0 : 1;
   }
   const bool two = d->two_cta != 0 && grid >= 2;
+  if (d->disp_mode != 0) {
+    // ---- fused dispatch: the A operand is a row buffer of the Buffer behind disp_ctx ----------
+    if (d->disp_ctx == nullptr) return fail(-20, "gemm: the fused dispatch needs the Buffer's context");
+    const BufferCtx& c = *(const BufferCtx*)d->disp_ctx;
+    if (c.virt) return fail(-21, "gemm: the fused dispatch runs one rank per launch (no virtual groups)");
+    if (c.token_padding % BM != 0)
+      return fail(-22, "gemm: the fused dispatch needs token_padding %% %d == 0 (tiles must not straddle groups)", BM);
+    if (d->nseg != 1 || !d->b_mn || (d->epi != EPI_SWIGLU && d->epi != EPI_BF16))
+      return fail(-23, "gemm: the fused dispatch feeds the gate/up (SwiGLU) and the down-dgrad GEMMs only");
+    uint8_t* rows = (uint8_t*)c.shard_base(d->disp_shard);
+    const long long row_bytes = (long long)c.H * 2;
+    if (rows == nullptr || (const uint8_t*)d->a[0] != rows + (size_t)c.rank * c.hidden_stride * row_bytes)
+      return fail(-24, "gemm: with the fused dispatch the A operand must be this rank's row buffer %d", d->disp_shard);
+    const int nsplit = (int)((row_bytes + FD_PART_CAP - 1) / FD_PART_CAP);
+    if (row_bytes % (16 * nsplit) != 0)
+      return fail(-25, "gemm: a row of %lld bytes cannot travel in %d equal 16-byte multiples", row_bytes, nsplit);
+    FusedDispatch& f = kp.disp;
+    f.arrive = c.meta + (size_t)c.rank * c.meta_stride + c.ml.arrive_off;
+    f.expect = BM * nsplit;
+    f.nsplit = nsplit; f.row_bytes = (int)row_bytes;
+    f.hidden = rows; f.meta = c.meta;
+    f.hidden_stride_bytes = (long long)c.hidden_stride * row_bytes; f.meta_stride = c.meta_stride;
+    f.weights_off = c.ml.weights_off; f.link_off = c.ml.link_off; f.src_off = c.ml.src_off;
+    f.arrive_off = c.ml.arrive_off; f.NvS = c.NvS;
+    f.N = (int)c.N; f.K = c.K; f.epn = c.epn; f.rank = c.rank; f.R = c.R; f.fresh = d->disp_fresh;
+    if (d->disp_mode == 2) {
+      if (d->disp_x == nullptr || d->disp_dst == nullptr || d->disp_order == nullptr || d->disp_zero_fill == nullptr)
+        return fail(-26, "gemm: the fused dispatch needs the token rows, the plan's dst, send order and padding ranges");
+      if (((uintptr_t)d->disp_x & 15) != 0) return fail(-27, "gemm: token rows must be 16-byte aligned");
+      f.x = (const uint8_t*)d->disp_x; f.w = d->disp_w; f.dst = d->disp_dst; f.order = d->disp_order;
+      f.zero_fill = d->disp_zero_fill;
+    }
+    kp.timeout_ns = c.timeout_ns;      // waits on other ranks: the Buffer's budget, not the GEMM's
+    if (d->epi == EPI_SWIGLU) {
+      if (two) return launch_gemm2<false, true, EPI_SWIGLU, false, false, true>(kp, grid, stream);
+      return launch_gemm<false, false, true, EPI_SWIGLU, false, true>(kp, grid, stream);
+    }
+    if (two) return launch_gemm2<false, true, EPI_BF16, false, false, true>(kp, grid, stream);
+    return launch_gemm<false, false, true, EPI_BF16, false, true>(kp, grid, stream);
+  }
   if (d->epi == EPI_SWIGLU) {
     if (!d->b_mn) return fail(-6, "swiglu epilogue expects MN-major weights");
     if (two) return launch_gemm2<false, true, EPI_SWIGLU>(kp, grid, stream);

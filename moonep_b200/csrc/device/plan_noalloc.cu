@@ -131,6 +131,7 @@ extern "C" int mep_plan_local_noalloc(const int32_t* tpe_all, const int32_t* top
   p.topk = topk; p.tpe = nullptr; p.dst = dst; p.cu_seqlens = cu_seqlens; p.zero_fill = zero_fill;
   p.etc = etc; p.remote_stats = remote_stats;
   p.scratch = scratch; p.scratch_ints = NOALLOC_INTS;
+  p.send_order = nullptr; p.arrive_off = 0; p.n_arrive = 0;
   lp.tpe_all = tpe_all; lp.rank = rank; lp.status_out = status;
   const size_t smem = sizeof(int32_t) * (2 * (size_t)E + 4 * (size_t)R + (size_t)PLAN_WARPS * R);
   if (smem > 48 * 1024) {

@@ -63,6 +63,10 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) ep_plan_kernel(const PlanPara
   __syncthreads();
   for (int e = tid; e < E; e += PLAN_THREADS) hist_g[(size_t)c * E + e] = cnt[e];
   if (c == 0) {
+    // arrival counters of the fused dispatch -> GEMM path start at zero; clearing them before
+    // the exchange orders the clear before every peer's first increment of this step
+    int32_t* arrive = sc.meta + (size_t)rank * sc.meta_stride + p.arrive_off;
+    for (int i = tid; i < p.n_arrive; i += PLAN_THREADS) arrive[i] = 0;
     cta_cross_rank_exchange(sc, 1);
     plan_solve(p, rank, sc.meta + (size_t)rank * sc.meta_stride + tbl_off, smem);
   }
@@ -79,7 +83,28 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) ep_plan_kernel(const PlanPara
     for (int cc = 0; cc < c; ++cc) base += hist_g[(size_t)cc * E + e];
     cnt[e] = base;
   }
+  // sending order: exclusive prefix of my per-expert counts in the permuted expert order
+  int32_t* pperm = smem + E;
+  if (p.send_order != nullptr) {
+    const int32_t* my_tpe = p.tpe + (size_t)vr * E;
+    for (int e = tid; e < E; e += PLAN_THREADS) pperm[send_perm(e, p.epn, R, rank)] = my_tpe[e];
+  }
   __syncthreads();
+  if (warp == 0 && p.send_order != nullptr) {
+    int run = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int n = e < E ? pperm[e] : 0;
+      int incl = n;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      if (e < E) pperm[e] = run + incl - n;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
   // stable rank of every entry among the entries of its expert (one warp, in order)
   if (warp == 0) {
     for (int64_t b = i0; b < i1; b += 32) {
@@ -114,29 +139,37 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) ep_plan_kernel(const PlanPara
     int64_t row = (int64_t)expert_off[(size_t)dest * E + e] + (g - prev);
     if (row < 0 || row >= p.NvS) { report_failure(sc, ST_BAD_INDEX, 21, dest, (int)row, (int)p.NvS); row = 0; }
     dst[i] = (int)((int64_t)dest * p.NvS + row);
+    if (p.send_order != nullptr) {
+      const int mine_before = rank > 0 ? tpe_cumsum[(size_t)(rank - 1) * E + e] : 0;
+      const int64_t pos = (int64_t)pperm[send_perm(e, p.epn, R, rank)] + (g - mine_before);
+      if (pos >= 0 && pos < p.N) p.send_order[(size_t)vr * p.N + pos] = (int32_t)i;
+      else report_failure(sc, ST_BAD_INDEX, 22, e, (int)pos, (int)p.N);
+    }
   }
   __syncthreads();
-  // duplicate canonicalisation + chain links, one thread per token
-  for (int t = tok0 + tid; t < tok1; t += PLAN_THREADS) {
+  // duplicate canonicalisation + chain links: K lanes per token (32 / K tokens per warp), the
+  // lanes of a token that share a destination rank find one another with match.any, so nothing
+  // is kept in per-thread arrays
+  const int tpw = 32 / K;
+  const int tl = lane / K, k = lane - tl * K;
+  for (int t0 = tok0 + warp * tpw; t0 < tok1; t0 += PLAN_WARPS * tpw) {
+    const int t = t0 + tl;
+    const bool valid = tl < tpw && t < tok1;
     int32_t* d = dst + (size_t)t * K;
-    int raw[MAX_TOPK];
-    int dr[MAX_TOPK];
-#pragma unroll 4
-    for (int k = 0; k < K; ++k) {
-      raw[k] = d[k];
-      dr[k] = (int)(raw[k] / p.NvS);
-    }
-    for (int k = 0; k < K; ++k) {
-      bool dup = false;
-      for (int j = 0; j < k; ++j) dup |= dr[j] == dr[k];
-      int next = LINK_NONE;
-      for (int j = K - 1; j > k; --j)
-        if (dr[j] == dr[k]) next = (int)(raw[j] - (int64_t)dr[j] * p.NvS);
-      int64_t row = raw[k] - (int64_t)dr[k] * p.NvS;
-      int32_t* peer = sc.meta + (size_t)dr[k] * sc.meta_stride;
+    const int raw = valid ? d[k] : 0;
+    const int dr = valid ? (int)(raw / p.NvS) : 0;
+    const unsigned m = __match_any_sync(0xffffffffu, valid ? ((tl << 8) | dr) : (0x40000000 | lane));
+    const bool dup = (m & ((1u << lane) - 1u)) != 0u;
+    const unsigned above = lane < 31 ? (m & ~((2u << lane) - 1u)) : 0u;
+    const int nl = above ? __ffs(above) - 1 : lane;
+    const int raw_next = __shfl_sync(0xffffffffu, raw, nl);
+    if (valid) {
+      const int next = above ? (int)(raw_next - (int64_t)dr * p.NvS) : LINK_NONE;
+      const int64_t row = raw - (int64_t)dr * p.NvS;
+      int32_t* peer = sc.meta + (size_t)dr * sc.meta_stride;
       peer[p.link_off + row] = next | (dup ? LINK_DUP_BIT : 0);
       peer[p.src_off + row] = (int32_t)((int64_t)rank * p.N + (int64_t)t * K + k);
-      if (dup) d[k] = -raw[k] - 1;
+      if (dup) d[k] = -raw - 1;
     }
   }
 }
@@ -152,12 +185,13 @@ int64_t mep_plan_smem_bytes(int R, int E) {
   return (int64_t)sizeof(int32_t) * (2 * (int64_t)E + 4 * R + (int64_t)PLAN_WARPS * R);
 }
 
-// Fresh plan for this rank (or for all virtual ranks).  Leaves the chain links in the peers'
+// Fresh plan for this rank (or for all virtual ranks).  send_order [Rv][N] may be null (it is
+// only needed by the fused dispatch -> GEMM path).  Leaves the chain links in the peers'
 // meta chunks; they become visible with the next cross-rank barrier (the dispatch kernel's
 // exit barrier, or an explicit mep_launch_sync).
 int mep_launch_plan(const void* ctx_, const int32_t* topk, const int32_t* tpe, int32_t* dst,
                     int32_t* cu_seqlens, int32_t* zero_fill, int32_t* etc, int32_t* remote_stats,
-                    cudaStream_t stream) {
+                    int32_t* send_order, cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   PlanParams p;
   p.sync = c.sync(KID_PLAN);
@@ -167,6 +201,7 @@ int mep_launch_plan(const void* ctx_, const int32_t* topk, const int32_t* tpe, i
   p.topk = topk; p.tpe = tpe; p.dst = dst; p.cu_seqlens = cu_seqlens; p.zero_fill = zero_fill;
   p.etc = etc; p.remote_stats = remote_stats;
   p.scratch = c.plan_scratch; p.scratch_ints = c.plan_scratch_ints;
+  p.send_order = send_order; p.arrive_off = c.ml.arrive_off; p.n_arrive = (int)(c.NvS / 128 + 1);
   size_t smem = (size_t)mep_plan_smem_bytes(c.R, c.E);
   static thread_local size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {

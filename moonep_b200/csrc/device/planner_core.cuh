@@ -23,7 +23,23 @@ struct PlanParams {
   int32_t* remote_stats;    // [Rv][2]
   int32_t* scratch;         // [Rv][scratch_ints]
   int64_t scratch_ints;
+  // Fused dispatch -> GEMM path (both optional; null / 0 when unused).
+  // send_order [Rv][N]: this rank's entries in the order in which its copy warps send them:
+  // by local expert index first (round j = e % epn), inside a round by home rank starting at
+  // the sender's own, then by token.  Every destination therefore receives its group j from all
+  // sources at about the same time, which is the order in which its GEMM consumes the groups.
+  int32_t* send_order;
+  int64_t arrive_off;       // ARRIVE counters in the meta chunk, cleared before the exchange
+  int n_arrive;
 };
+
+// Position of expert e in the sending order of `rank` (see PlanParams::send_order).
+MEP_HD int send_perm(int e, int epn, int R, int rank) {
+  const int h = e / epn, j = e - h * epn;
+  int rot = h - rank;
+  if (rot < 0) rot += R;
+  return j * R + rot;
+}
 
 constexpr int PLAN_THREADS = 512;
 constexpr int PLAN_WARPS = PLAN_THREADS / 32;

@@ -39,7 +39,7 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
     delete c;
     return nullptr;
   }
-  c->hidden = hidden; c->hidden_stride = hidden_stride_rows;
+  c->hidden = hidden; c->hidden2 = nullptr; c->hidden_stride = hidden_stride_rows;
   c->meta = (int32_t*)meta; c->meta_stride = meta_stride_ints;
   c->ml = meta_layout(c->NvS, R, E);
   c->sync_state = (int32_t*)sync_state; c->status = (int32_t*)status;
@@ -55,14 +55,12 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
 
 void mep_ctx_destroy(void* ctx) { delete (BufferCtx*)ctx; }
 
-// Points the context at another symmetric row buffer of the same geometry (a Buffer may own a
-// second shard so that a forward dispatch can stay in place while backward reuses the first).
-// Host-side state only: launches already issued keep the pointer they were given.
-int mep_ctx_set_hidden(void* ctx, void* hidden, int64_t hidden_stride_rows) {
+// Registers the second symmetric row buffer (same geometry as the first).  Launchers select a
+// buffer with their `shard` argument; nothing in the context is switched around a launch.
+int mep_ctx_set_second_shard(void* ctx, void* hidden2) {
   BufferCtx* c = (BufferCtx*)ctx;
-  if (c == nullptr || hidden == nullptr) return fail(-1, "ctx: set_hidden needs a context and a buffer");
-  c->hidden = hidden;
-  c->hidden_stride = hidden_stride_rows;
+  if (c == nullptr || hidden2 == nullptr) return fail(-1, "ctx: set_second_shard needs a context and a buffer");
+  c->hidden2 = hidden2;
   return 0;
 }
 

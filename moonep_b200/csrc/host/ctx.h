@@ -20,6 +20,7 @@ struct BufferCtx {
   int E, epn, S, K, H, token_padding, num_sms, num_sms_local, num_sms_weights;
   int64_t N, NvS;
   void* hidden;            // bf16 [R][hidden_stride_rows][H], symmetric
+  void* hidden2;           // optional second row buffer of the same geometry (null until enabled)
   int64_t hidden_stride;   // rows between consecutive ranks' shards
   int32_t* meta;           // int32 [R][meta_stride], symmetric
   int64_t meta_stride;
@@ -32,6 +33,10 @@ struct BufferCtx {
   int sm_count;
 
   int Rv() const { return virt ? R : 1; }
+  // Row buffer that a launch with the given shard index works on (null when it does not exist).
+  // The choice is a launch ARGUMENT: nothing in the context changes between launches, so
+  // dispatches into different shards may be issued from different threads or streams.
+  void* shard_base(int shard) const { return shard == 0 ? hidden : (shard == 1 ? hidden2 : nullptr); }
   // channel 0: dispatch / combine; channel 1: prefetch_weight / reduce_grad.  Each channel has
   // its own flag slots, epoch and grid-barrier word, so one kernel of each family may be in
   // flight at the same time (on different streams) without disturbing the other's barriers.

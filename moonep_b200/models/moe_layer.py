@@ -43,6 +43,10 @@ class ExpertPools:
         self.names = ("gate", "up", "down")
         self.prefetch = {}
         self.reduce = {}
+        # the plan whose redundant experts' weights the prefetch slots hold right now.  Several
+        # layers share the pools, so a layer's backward pass finds another layer's weights there
+        # unless it was the last one to prefetch; it then prefetches again (see _MoEFn.backward)
+        self.prefetch_owner = None
         if R == 1:
             return
         for n in self.names:
@@ -72,37 +76,48 @@ class _MoEFn(torch.autograd.Function):
         with tr.span("f.router"):
             logits = gemm.dense(x, layer.w_router)                         # [S, E] fp32
             topk, w, tpe = ew.router_topk(logits, buf.K, layer.router_bias)
+        fused = layer.fused_dispatch
+        disp = None
         with tr.span("f.dispatch"):
-            if layer.hidden_in_place:      # rows stay in the second shard until backward has used them
+            shard = 1 if layer.hidden_in_place else 0
+            if layer.hidden_in_place and ctx.needs_input_grad[0]:
+                buf.claim_second_shard(layer)      # rows stay in the second shard until backward has used them
+            if fused:
+                # only the plan is made here: the rows travel inside the gate/up GEMM launch below
+                hidden, w_nvs, cu, plan, disp = buf.dispatch_fused_begin(x, w, topk, tpe, shard=shard)
+            elif layer.hidden_in_place:
                 hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe, zero_copy=True, shard=1)
             else:
                 hidden, w_nvs, cu, plan = buf.dispatch(x, w, topk, tpe)
+        wait_only = None if disp is None else dict(disp, mode=1)
         pools = layer.pools
         if pools is not None and pools.prefetch:
             # the owners push the redundant experts' weights on the comm stream while this stream
             # already runs the gate/up GEMM of the local experts (which need no prefetched weight)
             # on the SMs the copy kernel leaves free; the prefetch slots follow in a second launch
-            ev = buf.prefetch_weight(
-                plan, async_finish=True, local_gate_weight=layer.w_gate,
-                local_up_weight=layer.w_up, local_down_weight=layer.w_down,
-                gate_prefetch_buffer=pools.prefetch["gate"], up_prefetch_buffer=pools.prefetch["up"],
-                down_prefetch_buffer=pools.prefetch["down"])
+            ev = layer.prefetch(plan)
             slots = dict(g=pools.slot("gate"), u=pools.slot("up"), d=pools.slot("down"))
             split, cu_use = epn, cu
             with tr.span("f.gateup_local"):
                 outs = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu[:epn], row_scale=w_nvs,
-                                          save_gate_up=layer.training, grid=layer.overlap_grid())
+                                          save_gate_up=layer.training, grid=layer.overlap_grid(), dispatch=disp)
             with tr.span("f.wait_prefetch"):
                 torch.cuda.current_stream().wait_event(ev)
             with tr.span("f.gateup_slots"):
                 act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu, wg_slot=slots["g"],
                                                    wu_slot=slots["u"], split=epn, row_scale=w_nvs,
-                                                   save_gate_up=layer.training, out=outs, g_begin=epn)
+                                                   save_gate_up=layer.training, out=outs, g_begin=epn,
+                                                   dispatch=wait_only)
         else:
             slots = dict(g=None, u=None, d=None)
             split, cu_use = None, cu[:epn]
-            act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use, row_scale=w_nvs,
-                                               save_gate_up=layer.training)
+            with tr.span("f.gateup"):
+                act, gate, up = gemm.gateup_swiglu(hidden, layer.w_gate, layer.w_up, cu_use, row_scale=w_nvs,
+                                                   save_gate_up=layer.training, dispatch=disp)
+        if fused:
+            w_nvs = buf.dispatch_fused_end(plan, disp)     # plan records + a private copy of the weights
+            if not layer.hidden_in_place:
+                hidden = hidden.clone()
         if layer.fused_combine:
             # down GEMM fused with the combine all-to-all: the epilogue stores every result row
             # into its entry's slot on the token's home rank while later tiles are still computing
@@ -133,10 +148,34 @@ class _MoEFn(torch.autograd.Function):
         # combine backward = dispatch with the saved plan; the view is consumed before the shard
         # is overwritten further down (same stream)
         tr = layer.tracer
+        disp = None
         with tr.span("b.dispatch"):
-            d_out, _, _, _ = buf.dispatch(dy, plan=plan, zero_copy=True)
+            if layer.fused_dispatch:    # dy travels inside the down-dgrad GEMM launch below
+                d_out, _, _, _, disp = buf.dispatch_fused_begin(dy, plan=plan)
+            else:
+                d_out, _, _, _ = buf.dispatch(dy, plan=plan, zero_copy=True)
+        ev_p = None
+        if have_slots and pools.prefetch_owner is not plan:
+            # Another layer's forward pass has refilled the shared prefetch slots since this
+            # layer's own: bring this plan's redundant experts' weights back before the dgrad
+            # GEMMs read them.  Issued after the dispatch entry above, whose barrier guarantees
+            # that no rank still reads the slots for a later layer's backward pass.  In fused-SGD
+            # mode the experts that have replicas are exactly those that keep their weights until
+            # sgd_step, so the copies are the weights forward used.
+            with tr.span("b.reprefetch"):
+                ev_p = layer.prefetch(plan)
         with tr.span("b.down_dgrad"):
-            d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split)
+            if ev_p is None:
+                d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split, dispatch=disp)
+            else:      # local experts first, next to the copy kernel; the slot groups once it is done
+                d_act = gemm.down_dgrad(d_out, layer.w_down, cu[:buf.epn], grid=layer.overlap_grid(),
+                                        dispatch=disp)
+                torch.cuda.current_stream().wait_event(ev_p)
+                d_act = gemm.down_dgrad(d_out, layer.w_down, cu, wd_slot=slot("down"), split=split,
+                                        out=d_act, g_begin=buf.epn,
+                                        dispatch=None if disp is None else dict(disp, mode=1))
+        if disp is not None:
+            buf.dispatch_fused_end(plan, disp)
         acc = layer.accumulate_grads
         fused_lr = layer.fused_sgd_lr
         do_reduce = have_slots and bool(pools.reduce)
@@ -166,6 +205,8 @@ class _MoEFn(torch.autograd.Function):
             with tr.span("b.wgrad_gateup"):
                 gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split, accumulate=acc)
                 gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, accumulate=acc)
+            if layer.hidden_in_place:  # the forward rows have had their last reader
+                buf.release_second_shard(layer)
             # the replicas' weight grads travel home on the comm stream while this stream computes dX
             if do_reduce:
                 ev_r = buf.reduce_grad(plan, async_finish=True, local_gate_grad=layer.g_gate,
@@ -219,6 +260,8 @@ class _MoEFn(torch.autograd.Function):
                                                      async_finish=True, zero_consumed=zc)
             gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, sgd=sgd(layer.w_up),
                        grid=layer.overlap_grid() if do_reduce else 0)
+        if layer.hidden_in_place:      # the forward rows have had their last reader
+            layer.buf.release_second_shard(layer)
         if do_reduce:         # and the up grads under the combine and the router backward
             ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
                                                  async_finish=True, zero_consumed=zc)
@@ -230,13 +273,20 @@ class MoELayer:
 
     def __init__(self, buf: Buffer, Hp: int, pools: Optional[ExpertPools] = None, *, seed: int = 0,
                  router_bias: Optional[torch.Tensor] = None, init_std: float = 0.02,
-                 train: bool = True, fused_combine: bool = True, hidden_in_place: bool = False):
+                 train: bool = True, fused_combine: bool = True, hidden_in_place: bool = False,
+                 fused_dispatch: Optional[bool] = None):
         assert not buf.virtual, "MoELayer runs one rank per process"
         assert buf.token_padding % 64 == 0, "the grouped GEMM needs token_padding % 64 == 0"
         assert buf.H % 128 == 0 and Hp % 64 == 0
         self.buf, self.pools, self.Hp = buf, pools, Hp
         self.training, self.accumulate_grads = train, False
         self.fused_combine = fused_combine
+        # dispatch all-to-all inside the consuming GEMM launch (forward: gate/up, backward: down
+        # dgrad) instead of a kernel of its own followed by a barrier; default: whenever the
+        # Buffer's shape allows it
+        ok = buf.fused_dispatch_supported()
+        assert not fused_dispatch or ok, "this Buffer's shape cannot use the fused dispatch"
+        self.fused_dispatch = ok if fused_dispatch is None else bool(fused_dispatch)
         # set to a learning rate to run the SGD step of the expert weights inside the weight-grad
         # epilogues of the next backward pass (see ``fuse_sgd``)
         self.fused_sgd_lr: Optional[float] = None
@@ -247,8 +297,11 @@ class MoELayer:
         # The dispatched rows are an activation that backward needs again, while backward's own
         # dispatch reuses the Buffer's row shard; by default forward therefore copies them out.
         # With ``hidden_in_place`` the Buffer gets a second shard for the forward rows and the copy
-        # (NvS x H bf16 read + written) is saved.  Valid as long as this layer's backward runs
-        # before its next forward (no second forward in between, e.g. for recomputation).
+        # (NvS x H bf16 read + written) is saved.  The Buffer has ONE second shard: it belongs to
+        # this layer from its forward pass until its backward pass has read the rows for the last
+        # time, so only one layer per Buffer may use the flag between a forward and its backward
+        # (a second layer's forward raises instead of overwriting the rows), and this layer's
+        # backward must run before its next forward.
         self.hidden_in_place = hidden_in_place
         if hidden_in_place:
             buf.enable_second_shard()
@@ -267,6 +320,17 @@ class MoELayer:
             self.g_router = z(1, H, E)
             self.g_gate, self.g_up, self.g_down = z(epn, H, Hp), z(epn, H, Hp), z(epn, H, Hp)
         self.last_plan = None
+
+    def prefetch(self, plan):
+        """``prefetch_weight`` of this layer's experts for ``plan`` on the comm stream; returns the
+        event and records the plan as the owner of the shared prefetch slots."""
+        pools = self.pools
+        ev = self.buf.prefetch_weight(
+            plan, async_finish=True, local_gate_weight=self.w_gate, local_up_weight=self.w_up,
+            local_down_weight=self.w_down, gate_prefetch_buffer=pools.prefetch["gate"],
+            up_prefetch_buffer=pools.prefetch["up"], down_prefetch_buffer=pools.prefetch["down"])
+        pools.prefetch_owner = plan
+        return ev
 
     def overlap_grid(self) -> int:
         """CTAs a GEMM may use while a weight op (prefetch / reduce) runs next to it."""

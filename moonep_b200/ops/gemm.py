@@ -49,7 +49,9 @@ class _GemmDesc(ctypes.Structure):
         ("push_rank_stride", ctypes.c_int64), ("push_entries", ctypes.c_int32),
         ("push_ranks", ctypes.c_int32), ("two_cta", ctypes.c_int32), ("pad2_", ctypes.c_int32),
         ("sgd_w", ctypes.c_void_p), ("sgd_keep", ctypes.c_void_p), ("sgd_lr", ctypes.c_float),
-        ("pad3_", ctypes.c_int32),
+        ("disp_mode", ctypes.c_int32), ("disp_ctx", ctypes.c_void_p), ("disp_x", ctypes.c_void_p),
+        ("disp_w", ctypes.c_void_p), ("disp_dst", ctypes.c_void_p), ("disp_order", ctypes.c_void_p),
+        ("disp_zero_fill", ctypes.c_void_p), ("disp_fresh", ctypes.c_int32), ("disp_shard", ctypes.c_int32),
     ]
 
 
@@ -70,11 +72,18 @@ def status_word(device) -> torch.Tensor:
 
 def check_status(device="cuda") -> None:
     st = status_word(device).tolist()
+    if st[0] == 5:
+        raise RuntimeError(f"grouped GEMM with fused dispatch: the rows of block {st[4]} never arrived "
+                           f"(CTA {st[3]} saw {st[5]} of {st[6]} row parts)")
     if st[0] != 0:
         raise RuntimeError(f"grouped GEMM: bounded wait expired (code {st[0]}, where {st[2]}, CTA {st[3]})")
 
 
-DEBUG_MODE = 0   # kernel timing experiments only (see GemmKParams::debug); 0 in normal use
+def reset_status(device="cuda") -> None:
+    status_word(device).zero_()
+
+
+PLAIN_EPILOGUE = False   # A/B switch of benchmarks: per-row 16-byte stores instead of staged TMA stores
 # CTA pairs (tcgen05 cta_group::2: clusters of two CTAs issue one 256-row MMA and each stages only
 # half of the B tile, which cuts the shared-memory reads per MMA from 12 KB to 8 KB, the limit of
 # the single-CTA kernel).  ``MOONEP_B200_TWO_CTA``: ``auto`` (default) uses pairs when the groups
@@ -90,7 +99,7 @@ PAIR_MIN_AVG_ROWS = 768
 
 def _launch(d: _GemmDesc) -> None:
     global _checked_layout
-    d.debug = DEBUG_MODE
+    d.debug = 16 if PLAIN_EPILOGUE else 0
     if TWO_CTA == 2:
         # token-major: a pair covers 256 rows of ONE group, so short groups would leave the second
         # CTA idle; the host only knows the average (over the local groups, the slot groups hold
@@ -122,7 +131,7 @@ def _groups(cu_seqlens, rows):
 
 
 def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_expert, b_mn, epi,
-                 outs, ldc, row_scale=None, total_rows=None, grid=0, push=None, g_begin=0):
+                 outs, ldc, row_scale=None, total_rows=None, grid=0, push=None, g_begin=0, dispatch=None):
     d = _GemmDesc()
     d.mode, d.epi, d.b_mn, d.nseg = 0, epi, int(b_mn), len(a_segs)
     cu_ptr, ngroups = _groups(cu_seqlens, None)
@@ -167,17 +176,29 @@ def _tokens_gemm(a_segs, b_sel, b_slot_sel, cu_seqlens, split, N, K, rows_per_ex
         d.push_base = push["push_base"].data_ptr()
         d.push_rank_stride = push["push_rank_stride"]
         d.push_entries, d.push_ranks = push["push_entries"], push["push_ranks"]
+    if dispatch is not None:
+        # the all-to-all that produces A runs inside this launch (``Buffer.dispatch_fused_begin``)
+        d.disp_mode, d.disp_ctx = int(dispatch["mode"]), dispatch["ctx"]
+        d.disp_fresh, d.disp_shard = int(dispatch["fresh"]), int(dispatch["shard"])
+        if d.disp_mode == 2:
+            d.disp_x = dispatch["x"].data_ptr()
+            d.disp_w = None if dispatch["w"] is None else dispatch["w"].data_ptr()
+            d.disp_dst, d.disp_order = dispatch["dst"].data_ptr(), dispatch["order"].data_ptr()
+            d.disp_zero_fill = dispatch["zero_fill"].data_ptr()
     _launch(d)
 
 
 def gateup_swiglu(x, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=None,
-                  row_scale=None, save_gate_up=True, out=None, g_begin=0, grid=0):
+                  row_scale=None, save_gate_up=True, out=None, g_begin=0, grid=0, dispatch=None):
     """``act[rows,H'] = silu(x Wg[g]) * (x Wu[g]) * row_scale``; also returns bf16 gate / up.
 
     ``x`` [rows, H]; ``wg``/``wu`` [G0, H, H'] (+ optional slot tensors for groups >= split).
     ``out=(act, gate, up)`` reuses existing outputs and ``g_begin`` skips the first groups, so the
     local experts and the prefetch slots can be computed by two launches; ``grid`` limits the
-    number of CTAs (to leave SMs to a concurrent communication kernel)."""
+    number of CTAs (to leave SMs to a concurrent communication kernel).  ``dispatch`` (from
+    ``Buffer.dispatch_fused_begin``) makes this launch carry the dispatch all-to-all itself: ``x``
+    must be the Buffer's row-buffer view, a seventh warp per CTA sends this rank's tokens, and
+    tiles are computed as their rows arrive (``dict(disp, mode=1)`` only waits for arrivals)."""
     rows, H = x.shape
     Hp = wg.shape[2]
     assert wg.shape[1] == H and wu.shape == wg.shape
@@ -190,7 +211,7 @@ def gateup_swiglu(x, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, split=No
     if row_scale is not None:
         assert row_scale.dtype == torch.float32 and row_scale.numel() >= rows
     _tokens_gemm([x], [wg, wu], [wg_slot, wu_slot], cu_seqlens, split, Hp, H, H, True, EPI_SWIGLU,
-                 [gate, up, act], Hp, row_scale, grid=grid, g_begin=g_begin)
+                 [gate, up, act], Hp, row_scale, grid=grid, g_begin=g_begin, dispatch=dispatch)
     return act, gate, up
 
 
@@ -211,12 +232,16 @@ def down(act, wd, cu_seqlens, *, wd_slot=None, split=None, out=None, push=None):
     return y
 
 
-def down_dgrad(dy, wd, cu_seqlens, *, wd_slot=None, split=None):
-    """``dact[rows,H'] = dy[rows,H] Wd[g]``."""
+def down_dgrad(dy, wd, cu_seqlens, *, wd_slot=None, split=None, out=None, g_begin=0, grid=0, dispatch=None):
+    """``dact[rows,H'] = dy[rows,H] Wd[g]``.  ``out`` / ``g_begin`` / ``grid`` / ``dispatch`` as in
+    :func:`gateup_swiglu`: the local experts and the prefetch slots may be two launches, and the
+    launch may carry the dispatch of ``dy`` itself."""
     rows, H = dy.shape
     Hp = wd.shape[2]
-    out = torch.empty(rows, Hp, dtype=torch.bfloat16, device=dy.device)
-    _tokens_gemm([dy], [wd], [wd_slot], cu_seqlens, split, Hp, H, H, True, EPI_BF16, [out], Hp)
+    if out is None:
+        out = torch.empty(rows, Hp, dtype=torch.bfloat16, device=dy.device)
+    _tokens_gemm([dy], [wd], [wd_slot], cu_seqlens, split, Hp, H, H, True, EPI_BF16, [out], Hp,
+                 grid=grid, g_begin=g_begin, dispatch=dispatch)
     return out
 
 

@@ -31,6 +31,9 @@ class CommPlan:
     NvS: int
     K: int
     src_info: Optional[torch.Tensor] = None   # [NvS] int32: owner entry of every received row
+    # [N] int32: this rank's entries in the order in which the fused dispatch -> GEMM path sends
+    # them (by local expert index, then home rank rotated by this rank, then token)
+    send_order: Optional[torch.Tensor] = None
     _dedup_cache: dict = field(default_factory=dict, compare=False, repr=False)
 
     def clone(self) -> "CommPlan":
@@ -43,6 +46,7 @@ class CommPlan:
             cu_seqlens=self.cu_seqlens.clone(),
             link=self.link.clone(),
             src_info=None if self.src_info is None else self.src_info.clone(),
+            send_order=None if self.send_order is None else self.send_order.clone(),
             _dedup_cache={},
         )
 

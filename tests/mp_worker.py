@@ -191,6 +191,50 @@ def layer_check(R, rank):
     buf.destroy()
 
 
+def fused_dispatch_check(R, rank):
+    """The dispatch that runs inside the gate/up (forward) and down-dgrad (backward) GEMM launches
+    must give bit-identical results to the stand-alone dispatch kernel, also with redundant
+    experts (local groups and prefetch slots are then two launches) and step after step."""
+    from moonep_b200.models.moe_layer import ExpertPools, MoELayer
+    from moonep_b200.ops import gemm
+    S, H, Hp, K = 512, 1024, 256, 4
+    E = 4 * R
+    buf = Buffer(S, H, K, E, R, num_sms=8, token_padding=128, timeout_s=10.0)
+    assert buf.fused_dispatch_supported()
+    pools = ExpertPools(R, E // R, H, Hp, buf.group, rank)
+    bias = torch.zeros(E, device="cuda")
+    bias[: E // R] = 1.5                       # overload rank 0: redundant experts, prefetch slots
+    g = torch.Generator(device="cuda").manual_seed(70 + rank)
+    x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    dy = torch.randn(S, H, device="cuda", generator=g).bfloat16()
+    res, used = [], 0
+    for fused in (False, True):
+        layer = MoELayer(buf, Hp, pools, seed=9, init_std=0.05, router_bias=bias, fused_dispatch=fused,
+                         hidden_in_place=True)
+        assert layer.fused_dispatch == fused
+        for _ in range(3):
+            xo = x.clone().requires_grad_(True)
+            y = layer(xo)
+            y.backward(dy)
+            layer.sgd_step(0.05)
+        buf.check()
+        gemm.check_status()
+        used = int((layer.last_plan.experts_to_copy >= 0).sum())
+        res.append([y.detach().clone(), xo.grad.clone(), layer.w_gate.clone(), layer.w_up.clone(),
+                    layer.w_down.clone(), layer.w_router.clone(), layer.last_plan.link.clone(),
+                    layer.last_plan.src_info.clone()])
+        torch.cuda.synchronize(); dist.barrier()
+    names = ["y", "dx", "w_gate", "w_up", "w_down", "w_router", "link", "src_info"]
+    bad = [n for n, a, b in zip(names, *res) if not torch.equal(a, b)]
+    all_ok(not bad, "fused dispatch vs stand-alone dispatch", f"differ: {bad}")
+    tot = torch.tensor([used], device="cuda")
+    dist.all_reduce(tot)
+    all_ok(int(tot) > 0, "fused dispatch check must exercise prefetch slots", f"slots used {int(tot)}")
+    if rank == 0:
+        print(f"fused dispatch R={R}: bit-identical over 3 steps, prefetch slots in use {int(tot) // R}", flush=True)
+    buf.destroy()
+
+
 def decoder_check(R, rank):
     """The fused EP path and the NCCL all-to-all path are two implementations of the same model:
     with identical parameters their first loss agrees, and both train."""
@@ -203,22 +247,47 @@ def decoder_check(R, rank):
     tgt = torch.randint(0, V, (S,), device="cuda", generator=g)
     bias = torch.zeros(E, device="cuda")
     bias[: E // R] = 1.0
-    out = {}
+    out, grads, slots = {}, {}, [None]
     for impl in ("fused", "nccl"):
         torch.manual_seed(3)
         if impl == "fused":
-            buf = Buffer(S, Hd, K, E, R, num_sms=8, token_padding=64, timeout_s=10.0)
+            # token_padding 128: the layers use the dispatch fused into their GEMMs, so the backward
+            # pass of layer 0 runs re-prefetch + fused dispatch + the two-launch down dgrad together
+            buf = Buffer(S, Hd, K, E, R, num_sms=8, token_padding=128, timeout_s=10.0)
             pools = ExpertPools(R, E // R, Hd, Hp, buf.group, rank)
             fac = lambda i: MoELayer(buf, Hp, pools, seed=20 + i, init_std=0.05, router_bias=bias)
         else:
             fac = lambda i: NcclMoELayer(S, Hd, K, E, Hp, seed=20 + i, init_std=0.05, router_bias=bias,
                                          token_padding=64)
         model = MoEDecoder(V, Hd, 2, 4, fac).cuda()
+        # one backward pass without an optimizer step: the two models have the same parameters and
+        # run the same GEMM kernels, so their gradients can be compared layer by layer.  Layer 0's
+        # redundant experts sit in prefetch slots that layer 1's forward pass has refilled by the
+        # time layer 0's backward pass needs them.
+        loss0 = model(tok, tgt)
+        loss0.backward()
+        torch.cuda.synchronize()
+        grads[impl] = dict(embed=model.embed.weight.grad.float().clone())
+        for i, m in enumerate(model.moe_layers()):
+            for n in ("g_gate", "g_up", "g_down", "g_router"):
+                grads[impl][f"{i}.{n}"] = getattr(m, n).clone()
+        if impl == "fused":
+            slots[0] = [int((m.last_plan.experts_to_copy >= 0).sum()) for m in model.moe_layers()]
+        for p_ in model.parameters():
+            p_.grad = None
         out[impl] = [float(model.train_step(tok, tgt, 0.05)) for _ in range(4)]
         if impl == "fused":
             buf.check()
             buf.destroy()
-    all_ok(abs(out["fused"][0] - out["nccl"][0]) < 2e-2, "fused vs nccl first loss", str(out))
+    tot = torch.tensor(slots[0], device="cuda")
+    dist.all_reduce(tot)
+    all_ok(int(tot[0]) > 0, "layer 0 must use prefetch slots", f"slots per layer {tot.tolist()}")
+    worst = {}
+    for k, a in grads["fused"].items():
+        b = grads["nccl"][k]
+        worst[k] = float((a - b).abs().max()) / (float(b.abs().max()) + 1e-12)
+    all_ok(max(worst.values()) < 2e-2, "fused vs nccl gradients", str(worst))
+    all_ok(max(abs(a - b) for a, b in zip(out["fused"], out["nccl"])) < 3e-2, "fused vs nccl losses", str(out))
     all_ok(out["fused"][-1] < out["fused"][0] and out["nccl"][-1] < out["nccl"][0], "both train", str(out))
     if rank == 0:
         print(f"decoder R={R}: {out}", flush=True)
@@ -274,6 +343,8 @@ def main():
         comm_checks(R, rank)
     if what in ("all", "layer"):
         layer_check(R, rank)
+    if what in ("all", "fused"):
+        fused_dispatch_check(R, rank)
     if what in ("all", "decoder"):
         decoder_check(R, rank)
     if what == "leave":

@@ -21,7 +21,7 @@ def _run(n, what, port):
         f"worker failed:\n{res.stdout[-3000:]}\n{res.stderr[-3000:]}"
 
 
-@pytest.mark.parametrize("what,port", [("comm", 29611), ("layer", 29612), ("decoder", 29615), ("leave", 29616)])
+@pytest.mark.parametrize("what,port", [("comm", 29611), ("layer", 29612), ("fused", 29617), ("decoder", 29615), ("leave", 29616)])
 def test_two_gpus(what, port):
     _run(2, what, port)
 
