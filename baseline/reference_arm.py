@@ -227,6 +227,29 @@ def _run(args):
         losses.append(float(step(stage).item()))
 
     ms_e2e = timed(e2e, args.steps)
+    # ---- communication round trip at the same shape, as the main arm times it: plan + dispatch +
+    # prefetch_weight + combine, zero copy, issued serially ------------------------------------
+    rt = {}
+
+    def comm_round(i):
+        if not rt:
+            logits = (xs[0] @ w_router).float()
+            sel = logits if bias is None else logits + bias
+            topk = sel.topk(K, dim=1).indices
+            rt["w"] = torch.softmax(logits.gather(1, topk), dim=1).contiguous()
+            rt["topk"] = topk.to(torch.int32).contiguous()
+            rt["tpe"] = torch.bincount(rt["topk"].flatten(), minlength=E).to(torch.int32)
+        hid, wn, cu, plan = buf.dispatch(xs[0], rt["w"], rt["topk"], rt["tpe"], zero_copy=True,
+                                         router_weights_zero_copy=True)
+        if nslot:
+            buf.prefetch_weight(plan=plan, local_gate_weight=W["gate"][:epn], local_up_weight=W["up"][:epn],
+                                local_down_weight=W["down"][:epn], gate_prefetch_buffer=Wcomm["gate"],
+                                up_prefetch_buffer=Wcomm["up"], down_prefetch_buffer=Wcomm["down"])
+        buf.combine(plan=plan, hidden_nvsh=hid, zero_copy=True)
+
+    for i in range(3):
+        comm_round(i)
+    ms_comm = timed(comm_round, max(args.steps, 10))
     tokens = R * S
     out = {
         "metric": "moe_layer_train_tokens_per_s", "value": tokens / (ms_step / 1e3), "unit": "tokens/s",
@@ -241,6 +264,8 @@ def _run(args):
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": S * H * 2, "d2h_bytes_per_step": 4,
                 "loss_last": losses[-1] if losses else None},
+        "comm_roundtrip_us": ms_comm * 1e3,
+        "comm_roundtrip_what": "plan + dispatch + prefetch_weight + combine, zero-copy, max over ranks",
         "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 2 ** 30,
     }
     if rank == 0:

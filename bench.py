@@ -47,6 +47,9 @@ def parse():
                     help="CTAs of dispatch / combine (default: 32 with peers, 96 on one GPU, where they are local copies)")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="down GEMM into the shard + pull combine instead of the push epilogue")
+    ap.add_argument("--no-fused-dispatch", action="store_true",
+                    help="stand-alone dispatch kernels (all-to-all, barrier, duplicate expansion) before the "
+                         "gate/up and down-dgrad GEMMs instead of the dispatch carried by those GEMM launches")
     ap.add_argument("--copy-dispatch-out", action="store_true",
                     help="forward dispatch copies its rows out of the shard (instead of keeping them in a "
                          "second shard until backward is done)")
@@ -164,7 +167,8 @@ def run_ours(args):
                  num_sms_weights=args.weight_sms)
     pools = ExpertPools(R, e // R, h, hp, buf.group, rank) if R > 1 else None
     layer = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine,
-                     hidden_in_place=not args.copy_dispatch_out)
+                     hidden_in_place=not args.copy_dispatch_out,
+                     fused_dispatch=False if args.no_fused_dispatch else None)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     n_batches = 4
     host = [torch.randn(s, h, generator=torch.Generator().manual_seed(1000 * rank + i)).bfloat16().pin_memory()
@@ -306,6 +310,8 @@ def run_ours(args):
                        ", fp32 weight grads stored" if args.no_fused_sgd else
                        ", SGD applied in the weight-grad epilogues (fp32 accumulators; experts with "
                        "replicas store fp32 grads, reduce them home, then update)"),
+                   "dispatch": "inside the gate/up and down-dgrad GEMM launches (rows consumed as they arrive)"
+                   if layer.fused_dispatch else "stand-alone kernel + barrier before the GEMM",
                    "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",
                    "cuda_graph": graphed,
                    "l2": "working set per step (>= 8 GB of weights, grads and activations) exceeds the 126 MB L2; no explicit flush"},
