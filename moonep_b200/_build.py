@@ -32,6 +32,9 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fno-strict-aliasing",
     "-Xcompiler", "-Wno-psabi", "-DNDEBUG",
 ]
+# extra nvcc flags for one-off builds (e.g. -DMEP_GEMM_EXPERIMENTS, which compiles the timing
+# experiment switches of the GEMM in; a normal build has none of those branches)
+NVCC_FLAGS += os.environ.get("MOONEP_B200_NVCC_FLAGS", "").split()
 
 
 def _nvcc() -> str:

@@ -43,6 +43,7 @@ nat.declare("mep_meta_offsets", None, [L, I, I, ctypes.POINTER(ctypes.c_int64)])
 nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, I, P, L, P, L, P, P, P, L])
 nat.declare("mep_ctx_destroy", None, [P])
 nat.declare("mep_ctx_set_second_shard", I, [P, P])
+nat.declare("mep_ctx_set_pdl", None, [P, I])
 nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P, P])
 nat.declare("mep_launch_arrive_reset", I, [P, P])
 nat.declare("mep_launch_plan_snapshot", I, [P, P, P, P])
@@ -108,7 +109,10 @@ class Buffer:
         self.N = S * K
         self.token_padding = token_padding
         self.virtual = bool(virtual)
-        self.enable_pdl = enable_pdl     # accepted for signature parity; launches are plain
+        # programmatic dependent launch of the kernel chains plan -> dispatch -> expansion and
+        # pre-reduction -> pull combine (moonep/_common.py:393-406, api.py:622-626): each follower
+        # is scheduled while its predecessor still runs and waits on the device for its completion
+        self.enable_pdl = bool(enable_pdl)
         self.explicitly_destroy = explicitly_destroy
         self.device = torch.cuda.current_device()
         dev = torch.device("cuda", self.device)
@@ -181,6 +185,7 @@ class Buffer:
             self.status.data_ptr(), self.plan_scratch.data_ptr(), int(self.timeout_s * 1e9))
         if not self._ctx:
             raise RuntimeError(f"Buffer: {nat.last_error()}")
+        nat.call("mep_ctx_set_pdl", self._ctx, int(self.enable_pdl))
         self.comm_stream = torch.cuda.Stream(device=dev, priority=comm_stream_priority)
         self._stats = dict(dispatch=0, combine=0, prefetch_weight=0, reduce_grad=0,
                            bytes_dispatch=0, bytes_combine=0)

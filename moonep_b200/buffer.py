@@ -37,6 +37,7 @@ IP = ctypes.POINTER(ctypes.c_int)
 
 nat.declare("mep_driver_available", I, [])
 nat.declare("mep_vmm_supported", I, [I])
+nat.declare("mep_launch_multimem_bcast", I, [P, P, L, P])
 nat.declare("mep_fabric_supported", I, [I])
 nat.declare("mep_multicast_supported", I, [I])
 nat.declare("mep_vmm_granularity", L, [I, I])
@@ -135,8 +136,9 @@ def handle_type_for_group(group, device: int) -> str:
         ok = all(int(t.item()) for t in all_)
     else:
         ok = bool(int(mine.item()))
-    # A single host never needs fabric handles; prefer fds there, as they need no IMEX daemon.
-    return "fabric" if ok and os.environ.get("MOONEP_PREFER_FABRIC") == "1" else "fd"
+    # as in the reference (moonep/buffer.py:28-57): fabric handles iff every rank can really
+    # create one (the probe allocates a granule), POSIX file descriptors otherwise
+    return "fabric" if ok else "fd"
 
 
 def exchange_fds(fd: int, group, tag: str = "h") -> list[int]:
@@ -404,6 +406,8 @@ def create_nvl_dist_multicast_tensor(shape, dtype, local_rank=None, world_size=N
     want = os.environ.get("MOONEP_B200_NVLS") == "1"
     if R == 1 or not want or not nat.call("mep_multicast_supported", device):
         return t, None
+    if handle_type_for_group(group, device) == "fabric":
+        return t, None          # the overlay below shares its multicast object through file descriptors
     m: _Mapping = t._symm_mapping
     rank = dist.get_rank(group)
     gran = nat.call("mep_multicast_granularity", R, m.chunk_bytes)
@@ -468,6 +472,19 @@ def create_nvl_single_owner_tensor(shape, dtype, owner: int, group=None, device:
     t = _wrap(m, shape, dtype, rows)
     dist.barrier(group=group)
     return t[: shape[0]]
+
+
+def multimem_broadcast(alias: torch.Tensor, src: torch.Tensor, offset: int = 0) -> None:
+    """Store ``src`` (any 4-byte dtype, contiguous, local) through the multicast ``alias`` of a
+    symmetric tensor at element ``offset``: the words land at the same place in EVERY rank's chunk
+    (NVSwitch ``multimem.st``, the reference's plan broadcast, moonep/planning.py:147-156).  They
+    are visible on the other ranks after the caller's next cross-rank synchronisation."""
+    assert alias.element_size() == 4 and src.element_size() == 4 and src.is_contiguous() and src.is_cuda
+    assert 0 <= offset and offset + src.numel() <= alias.numel()
+    rc = nat.call("mep_launch_multimem_bcast", alias.data_ptr() + 4 * offset, src.data_ptr(), src.numel(),
+                  torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise SymmetricMemoryError(f"multimem broadcast: {nat.last_error()}")
 
 
 def release(t: torch.Tensor) -> None:

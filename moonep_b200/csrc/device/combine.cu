@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(PROLOGUE_THREADS) ep_combine_prologue_kernel(c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vr = blockIdx.y, rank = p.rank_base + vr;
   const int32_t* link = p.link + (size_t)vr * p.NvS;
+  pdl_launch_dependents();   // the pull kernel may set up its ring; it waits for this kernel to end
   int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
   if (rows > p.NvS) rows = p.NvS;
   uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
@@ -148,6 +149,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
     mbar_fence_init();
   }
   __syncthreads();
+  pdl_wait();                 // this rank's pre-reduction kernel has completed
   cross_rank_barrier(sc, 1);  // every rank's shard (and its pre-reduction) is final
 
   const int32_t* dst = p.dst + (size_t)vr * p.N;
@@ -326,8 +328,8 @@ static int launch_combine_t(const BufferCtx& c, CombineParams& p, size_t smem, c
     configured = smem;
   }
   dim3 grid(c.num_sms, c.Rv());
-  MEP_CUDA_OK(launch_coop((const void*)ep_combine_kernel<ST, NV>, grid, dim3(COMBINE_THREADS), smem,
-                          stream, p));
+  MEP_CUDA_OK(launch_chained((const void*)ep_combine_kernel<ST, NV>, grid, dim3(COMBINE_THREADS), smem,
+                             stream, p, /*coop=*/1, c.pdl));
   return 0;
 }
 

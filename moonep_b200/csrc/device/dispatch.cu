@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
     *reinterpret_cast<uint4*>(zero_row + i) = make_uint4(0, 0, 0, 0);
   fence_proxy_async_smem();
   __syncthreads();
+  pdl_launch_dependents();   // the expansion kernel may be scheduled; it waits for this one to end
+  pdl_wait();                // a preceding planner launch has completed: its plan is readable
   if (p.entry_barrier) cross_rank_barrier(sc, 1);
 
   const __nv_bfloat16* x = p.x + (size_t)vr * p.S * p.H;
@@ -179,6 +181,7 @@ __global__ void __launch_bounds__(EXPAND_THREADS) ep_expand_kernel(const ExpandP
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vr = blockIdx.y, rank = p.rank_base + vr;
   const int32_t* link = p.link + (size_t)vr * p.NvS;
+  pdl_wait();                // the dispatch kernel before this one has completed
   int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
   if (rows > p.NvS) rows = p.NvS;
   uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
@@ -248,8 +251,8 @@ static int launch_dispatch_t(const BufferCtx& c, DispatchParams& p, size_t smem,
     configured = smem;
   }
   dim3 grid(c.num_sms, c.Rv());
-  MEP_CUDA_OK(launch_coop((const void*)ep_dispatch_kernel<ST>, grid, dim3(DISPATCH_THREADS), smem,
-                          stream, p));
+  MEP_CUDA_OK(launch_chained((const void*)ep_dispatch_kernel<ST>, grid, dim3(DISPATCH_THREADS), smem,
+                             stream, p, /*coop=*/1, c.pdl && p.fresh));
   return 0;
 }
 
@@ -297,8 +300,8 @@ int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_s
   p.hidden = (__nv_bfloat16*)c.shard_base(shard); p.link = link; p.cu_seqlens = cu_seqlens;
   // latency-bound row walks: several CTAs per SM keep enough loads in flight
   dim3 grid(c.num_sms_local * 6, c.Rv());
-  ep_expand_kernel<<<grid, EXPAND_THREADS, 0, stream>>>(p);
-  MEP_CUDA_OK(cudaGetLastError());
+  MEP_CUDA_OK(launch_chained((const void*)ep_expand_kernel, grid, dim3(EXPAND_THREADS), 0, stream, p,
+                             /*coop=*/0, c.pdl));
   return 0;
 }
 

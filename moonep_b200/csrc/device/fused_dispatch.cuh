@@ -36,7 +36,6 @@
 namespace mep {
 
 constexpr int FD_PART_CAP = 7168;   // bytes of a ring stage; a row travels in nsplit equal parts
-constexpr int FD_LA = 2;            // loads issued ahead of the store being issued
 constexpr int FD_RUN = 8;           // consecutive entries per CTA and window
 
 struct FusedDispatch {
@@ -55,91 +54,101 @@ struct FusedDispatch {
   long long meta_stride;           // int32 elements
   long long weights_off, link_off, src_off, arrive_off, NvS;
   int N, K, epn, rank, R, fresh, row_bytes, nsplit;
+  int debug;   // timing experiments, compiled in only with -DMEP_GEMM_EXPERIMENTS (see fd_dbg)
 };
 
-// One warp.  `ring` holds NST stages of FD_PART_CAP bytes, `full` NST mbarriers (initialised with
-// count 1 by the caller), `slots` 2 * NST words of scratch.  `wait_full(bar, parity)` is the
-// caller's bounded mbarrier wait (returns false after a timeout or an abort).
+// Timing experiments (results are wrong when set): 1 = arrival signals without the release fence,
+// 4 = the copy warp issues no stores, 8 = neither loads nor stores.  A constant false in a normal build.
+#ifdef MEP_GEMM_EXPERIMENTS
+__device__ __forceinline__ bool fd_dbg(const FusedDispatch& d, int bit) { return (d.debug & bit) != 0; }
+#else
+__device__ __forceinline__ constexpr bool fd_dbg(const FusedDispatch&, int) { return false; }
+#endif
+
+// One warp.  `ring` holds NST stages of FD_PART_CAP bytes and `full` NST mbarriers (initialised
+// with count 1 by the caller): lane i < NST owns stage i.  The warp works in lockstep rounds of
+// NST units (a unit is one part of one row): every owning lane loads its unit into its stage,
+// waits for it, stores it to the destination, waits for that store to complete, and the lanes
+// whose units share a destination counter signal it with ONE release.  All per-unit scalar work
+// is thereby spread over NST lanes; NST * 7 KB per round trip of (load + remote store) latency
+// keeps 148 CTAs well above the NVLink rate.  `wait_full(bar, parity)` is the caller's bounded
+// mbarrier wait (false after a timeout or an abort).
 template <int NST, class WaitFn>
 __device__ __forceinline__ void fused_dispatch_copy_warp(const FusedDispatch& d, uint8_t* ring,
-                                                         uint64_t* full, unsigned long long* slots,
-                                                         int cta, int n_cta, WaitFn wait_full) {
-  static_assert(NST > FD_LA + 1, "the ring must hold the loads in flight and at least one store");
+                                                         uint64_t* full, int cta, int n_cta,
+                                                         WaitFn wait_full) {
+  static_assert(NST >= 1 && NST <= 32, "one lane per ring stage");
   const int lane = threadIdx.x & 31;
   const int part_bytes = d.row_bytes / d.nsplit;
   int32_t* my_meta = d.meta + (size_t)d.rank * d.meta_stride;
   uint8_t* my_rows = d.hidden + (size_t)d.rank * d.hidden_stride_bytes;
 
   // ---- padding rows of MY buffer: zeroed with plain stores, counted like arrivals ------------
-  for (int g0 = 0; g0 < 2 * d.epn; g0 += 32) {
-    const int g = g0 + lane;
-    int first_l = 0, n_l = 0;
-    if (g < 2 * d.epn) { first_l = d.zero_fill[2 * g]; n_l = d.zero_fill[2 * g + 1]; }
-    for (int j = 0; j < 32 && g0 + j < 2 * d.epn; ++j) {
-      const int first = __shfl_sync(0xffffffffu, first_l, j);
-      const int n = __shfl_sync(0xffffffffu, n_l, j);
-      if (n <= 0 || first < 0 || (long long)first + n > d.NvS) continue;
-      for (int r = first + cta; r < first + n; r += n_cta) {
-        uint4* row = reinterpret_cast<uint4*>(my_rows + (size_t)r * d.row_bytes);
-        for (int v = lane; v < d.row_bytes / 16; v += 32) row[v] = make_uint4(0, 0, 0, 0);
-        if (lane == 0) {
-          if (d.w != nullptr) my_meta[d.weights_off + r] = 0;
-          if (d.fresh) { my_meta[d.link_off + r] = LINK_NONE; my_meta[d.src_off + r] = -1; }
+  // Done in slices between the batches of entries below: the padding of local group j is needed
+  // when the GEMM reaches group j, which is when the senders reach round j of the sending order,
+  // and doing all of it up front would only delay the first groups.
+  auto do_pads = [&](int g_from, int g_to) {
+    for (int g0 = g_from; g0 < g_to; g0 += 32) {
+      const int g = g0 + lane;
+      int first_l = 0, n_l = 0;
+      if (g < g_to) { first_l = d.zero_fill[2 * g]; n_l = d.zero_fill[2 * g + 1]; }
+      for (int j = 0; j < 32 && g0 + j < g_to; ++j) {
+        const int first = __shfl_sync(0xffffffffu, first_l, j);
+        const int n = __shfl_sync(0xffffffffu, n_l, j);
+        if (n <= 0 || first < 0 || (long long)first + n > d.NvS) continue;
+        for (int r = first + cta; r < first + n; r += n_cta) {
+          uint4* row = reinterpret_cast<uint4*>(my_rows + (size_t)r * d.row_bytes);
+          for (int v = lane; v < d.row_bytes / 16; v += 32) row[v] = make_uint4(0, 0, 0, 0);
+          if (lane == 0) {
+            if (d.w != nullptr) my_meta[d.weights_off + r] = 0;
+            if (d.fresh) { my_meta[d.link_off + r] = LINK_NONE; my_meta[d.src_off + r] = -1; }
+          }
+          __syncwarp();
+          if (lane == 0) red_release_sys_add(my_meta + d.arrive_off + (r >> 7), d.nsplit);
         }
-        __syncwarp();
-        if (lane == 0) red_release_sys_add(my_meta + d.arrive_off + (r >> 7), d.nsplit);
       }
     }
-  }
+  };
 
   // ---- my entries: windows of n_cta * FD_RUN positions of the sending order -------------------
-  const long long win = (long long)n_cta * FD_RUN;
-  const long long n_win = (d.N + win - 1) / win;
-  long long n_ent = 0;     // entries of this CTA (a prefix of its window slots)
+  const int win = n_cta * FD_RUN;
+  const int n_win = (d.N + win - 1) / win;
+  int n_ent = 0;           // entries of this CTA (a prefix of its window slots)
   if (n_win > 0) {
-    const long long last0 = (n_win - 1) * win + (long long)cta * FD_RUN;
-    long long tail = d.N - last0;
+    int tail = d.N - ((n_win - 1) * win + cta * FD_RUN);
     tail = tail < 0 ? 0 : (tail > FD_RUN ? FD_RUN : tail);
     n_ent = (n_win - 1) * FD_RUN + tail;
   }
-  const long long n_units = n_ent * d.nsplit;
-  // lane 0's pipeline state
-  unsigned long long pend_ctr = 0ull;
-  int pend_cnt = 0;
+  const int n_units = n_ent * d.nsplit;
+  constexpr int PER_BATCH = 32 / NST * NST;        // units decoded at once, a multiple of NST
+  const int NvS = (int)d.NvS;
+  uint8_t* my_stage = ring + (size_t)(lane < NST ? lane : 0) * FD_PART_CAP;
+  uint64_t* my_full = &full[lane < NST ? lane : 0];
+  uint32_t parity = 0;     // of my_full: flips every time this lane has used its stage
   bool ok = true;
-  auto flush = [&]() {
-    if (pend_cnt > 0) {
-      fence_proxy_async();
-      red_release_sys_add(reinterpret_cast<int32_t*>(pend_ctr), pend_cnt);
-      pend_cnt = 0;
-    }
-  };
-  auto completed = [&](int stage) {       // the unit that used `stage` has fully landed
-    const unsigned long long ctr = slots[NST + stage];
-    if (ctr == 0ull) return;              // a unit that sent nothing
-    if (ctr != pend_ctr) { flush(); pend_ctr = ctr; }
-    ++pend_cnt;
-  };
-  auto store_unit = [&](long long v) {    // unit v's load has been issued: wait for it, send it on
-    const int sv = (int)(v % NST);
-    if (!wait_full(&full[sv], (uint32_t)(v / NST) & 1u)) { ok = false; return; }
-    bulk_s2g(reinterpret_cast<void*>(slots[sv]), ring + (size_t)sv * FD_PART_CAP, (uint32_t)part_bytes);
-    bulk_commit();
-  };
+  const int n_batches = (n_units + PER_BATCH - 1) / PER_BATCH;
+  int pad_g = d.epn < 2 ? d.epn : 2;       // local groups whose padding is done
+  int batch = 0;
+  do_pads(0, pad_g);
 
-  for (long long u0 = 0; u0 < n_units; u0 += 32) {
-    // ---- all lanes: decode 32 units (entry -> source row, destination row, counter) ----------
-    const long long u = u0 + lane;
+  for (int u0 = 0; u0 < n_units && ok; u0 += PER_BATCH, ++batch) {
+    {   // keep the padding two groups ahead of the senders' position in the sending order
+      int upto = (int)(((long long)(batch + 1) * d.epn) / n_batches) + 2;
+      upto = upto > d.epn ? d.epn : upto;
+      if (upto > pad_g) { do_pads(pad_g, upto); pad_g = upto; }
+    }
+    // ---- all lanes: decode up to PER_BATCH units (entry -> source, destination, counter) -----
+    const int u = u0 + lane;
     unsigned long long src = 0ull, dstp = 0ull, ctr = 0ull;
-    if (u < n_units) {
-      const long long ie = u / d.nsplit;
-      const int part = (int)(u - ie * d.nsplit);
-      const long long pos = (ie / FD_RUN) * win + (long long)cta * FD_RUN + (ie % FD_RUN);
+    if (lane < PER_BATCH && u < n_units) {
+      const int ie = u / d.nsplit;
+      const int part = u - ie * d.nsplit;
+      const int pos = (ie / FD_RUN) * win + cta * FD_RUN + (ie % FD_RUN);
       const int entry = d.order[pos];
       if ((unsigned)entry < (unsigned)d.N) {
         const int dv = d.dst[entry];
-        const long long raw = dv >= 0 ? dv : -(long long)dv - 1;
-        const long long dr = raw / d.NvS, row = raw - dr * d.NvS;
+        const int raw = dv >= 0 ? dv : -dv - 1;
+        const int dr = raw / NvS, row = raw - dr * NvS;
         if (dr < d.R) {
           const int tok = entry / d.K;
           src = (unsigned long long)(d.x + (size_t)tok * d.row_bytes + (size_t)part * part_bytes);
@@ -151,56 +160,46 @@ __device__ __forceinline__ void fused_dispatch_copy_warp(const FusedDispatch& d,
         }
       }
     }
-    __syncwarp();     // the weight stores above are ordered before lane 0's releases below
-    // ---- lane 0: feed the units through the ring ----------------------------------------------
-    const int nb = (int)((n_units - u0) < 32 ? (n_units - u0) : 32);
-    for (int l = 0; l < nb; ++l) {
-      const unsigned long long s_src = __shfl_sync(0xffffffffu, src, l);
-      const unsigned long long s_dst = __shfl_sync(0xffffffffu, dstp, l);
-      const unsigned long long s_ctr = __shfl_sync(0xffffffffu, ctr, l);
-      if (lane == 0 && ok) {
-        const long long uu = u0 + l;
-        const int s = (int)(uu % NST);
-        if (uu >= NST) {
-          // units 0 .. uu-FD_LA-1 have been committed; all but the most recent NST-FD_LA-1 of
-          // those groups are complete after this wait, i.e. every unit up to uu-NST
-          bulk_wait<NST - FD_LA - 1>();
-          completed(s);
-        }
-        if (s_src != 0ull) {
-          slots[s] = s_dst;
-          slots[NST + s] = s_ctr;
-          mbar_expect_tx(&full[s], (uint32_t)part_bytes);
-          bulk_g2s(ring + (size_t)s * FD_PART_CAP, reinterpret_cast<const void*>(s_src),
-                   (uint32_t)part_bytes, &full[s]);
+    __syncwarp();     // the weight stores above are ordered before the releases below
+    // ---- rounds of NST units: lane i < NST moves unit u0 + r0 + i through stage i ---------------
+    for (int r0 = 0; r0 < PER_BATCH && u0 + r0 < n_units; r0 += NST) {
+      const int from = r0 + (lane < NST ? lane : 0);
+      const unsigned long long s_src = __shfl_sync(0xffffffffu, src, from);
+      const unsigned long long s_dst = __shfl_sync(0xffffffffu, dstp, from);
+      const unsigned long long s_ctr = __shfl_sync(0xffffffffu, ctr, from);
+      const bool act = lane < NST && u0 + from < n_units && s_src != 0ull;
+      bool sent = false;
+      if (act) {
+        if (!fd_dbg(d, 8)) {
+          mbar_expect_tx(my_full, (uint32_t)part_bytes);
+          bulk_g2s(my_stage, reinterpret_cast<const void*>(s_src), (uint32_t)part_bytes, my_full);
+          sent = wait_full(my_full, parity);
+          parity ^= 1u;
+          if (sent && !fd_dbg(d, 4)) {
+            bulk_s2g(reinterpret_cast<void*>(s_dst), my_stage, (uint32_t)part_bytes);
+            bulk_commit();
+            bulk_wait<0>();          // complete, not just read: the rows may now be announced
+          }
         } else {
-          // an entry that failed its index checks: keep the ring in phase, send nothing
-          slots[s] = 0ull;
-          slots[NST + s] = 0ull;
-          mbar_arrive(&full[s]);
+          sent = true;
         }
-        if (uu >= FD_LA) {
-          const long long v = uu - FD_LA;
-          if (slots[v % NST] != 0ull) store_unit(v);
-          else { if (!wait_full(&full[v % NST], (uint32_t)(v / NST) & 1u)) ok = false; bulk_commit(); }
-        }
+        if (sent && !fd_dbg(d, 1)) fence_proxy_async();
       }
+      // a load that never landed ends this warp's work (the status is already recorded)
+      if (__any_sync(0xffffffffu, act && !sent)) ok = false;
+      // lanes whose units share a destination counter announce them with one release
+      const unsigned long long key = (act && sent) ? s_ctr : 0ull;
+      const unsigned grp = __match_any_sync(0xffffffffu, key);
+      if (key != 0ull && lane == __ffs(grp) - 1) {
+        if (fd_dbg(d, 1)) atomicAdd_system(reinterpret_cast<int*>(key), __popc(grp));
+        else red_release_sys_add(reinterpret_cast<int32_t*>(key), __popc(grp));
+      }
+      if (!ok) break;
     }
   }
-  if (lane == 0) {
-    if (ok) {
-      for (long long v = n_units > FD_LA ? n_units - FD_LA : 0; v < n_units && ok; ++v) {
-        if (slots[v % NST] != 0ull) store_unit(v);
-        else { if (!wait_full(&full[v % NST], (uint32_t)(v / NST) & 1u)) ok = false; bulk_commit(); }
-      }
-    }
-    bulk_wait<0>();        // also on an abort: nothing of this thread stays in flight
-    if (ok) {
-      for (long long v = n_units > NST ? n_units - NST : 0; v < n_units; ++v) completed((int)(v % NST));
-      flush();
-    }
-  }
+  if (lane < NST) bulk_wait<0>();
   __syncwarp();
+  do_pads(pad_g, 2 * d.epn);               // the rest, and the prefetch-slot groups (consumed last)
 }
 
 }  // namespace mep

@@ -46,6 +46,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "device/fused_dispatch.cuh"
@@ -104,6 +105,10 @@ struct GemmKParams {
   long long push_rank_stride;
   int push_entries, push_ranks;
   FusedDispatch disp;      // DISP kernels only
+  // DISP: budget of a wait for rows from other ranks.  It is shorter than timeout_ns, which bounds
+  // the waits that only follow from it (the MMA thread on the operand ring, the epilogue on the
+  // accumulator), so that a missing row is reported as what it is.
+  unsigned long long arrive_timeout_ns;
 };
 
 #ifdef MEP_GEMM_EXPERIMENTS
@@ -151,9 +156,11 @@ __device__ __forceinline__ bool arrive_wait(const int32_t* ctr, int expect, int 
   unsigned long long t0 = globaltimer_ns();
   unsigned spins = 0;
   while ((seen = ld_acquire_sys(ctr)) < expect) {
+    // many CTAs watch the same few counters while the senders' reductions land on them: back off
+    __nanosleep(500);
     if ((++spins & 63u) == 0) {
       if (*s_abort) return false;
-      if (globaltimer_ns() - t0 > p.timeout_ns) {
+      if (globaltimer_ns() - t0 > p.arrive_timeout_ns) {
         *s_abort = 1;
         if (p.status != nullptr && atomicCAS(p.status, 0, ST_TIMEOUT_ARRIVAL) == 0) {
           p.status[1] = KID_GEMM;
@@ -252,6 +259,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t s_tmem;
   __shared__ int s_abort;
+  __shared__ int s_groups_ready;   // DISP: written by the arrival watchers, read by the producer
   __shared__ int s_end[MAX_GROUPS];
   __shared__ int s_prefix[WGRAD ? 1 : MAX_GROUPS + 1];
   // per-warp staging of the fp32 epilogues: 32 x 33 floats token-major, a 4 KB swizzled block for
@@ -263,9 +271,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
   // staging of the bf16 epilogue: per warp one 32 x 64 block (128-byte rows, 128B swizzle)
   __shared__ __align__(1024) uint8_t s_out[(!WGRAD && EPI == EPI_BF16) ? 4 * 4096 : 16];
-  // fused dispatch: "landed" barriers of the copy ring, and per stage the destination / counter
+  // fused dispatch: "landed" barriers of the copy ring
   __shared__ __align__(8) uint64_t fd_full[DISP ? FD_NST : 1];
-  __shared__ unsigned long long fd_slots[DISP ? 2 * FD_NST : 1];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -280,6 +287,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     if constexpr (DISP) for (int a = 0; a < FD_NST; ++a) mbar_init(&fd_full[a], 1);
     mbar_fence_init();
     s_abort = 0;
+    s_groups_ready = 0;
   }
   // group table
   for (int g = tid; g < p.ngroups; g += (int)blockDim.x)
@@ -328,15 +336,36 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       tma_prefetch_desc(&p.b[0][0]);
       int it = 0;
       bool ok = true;
+      int groups_ready = 0;      // DISP: groups [0, groups_ready) are known to have arrived
       for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
         Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
         if (!t.valid) continue;
         const int kb_per_seg = WGRAD ? t.num_kb : (p.K + BK - 1) / BK;
         if constexpr (DISP) {
-          // the rows of this tile come from other ranks' copy warps: wait until all have landed
-          if (p.disp.arrive != nullptr && t.rows > 0) {
-            if (!arrive_wait(p.disp.arrive + (t.row0 >> 7), p.disp.expect, t.row0 >> 7, abortp, p)) break;
+          // The rows of this tile come from other ranks' copy warps.  The other lanes of this warp
+          // watch the arrival counters group by group (below) and publish how many groups are
+          // complete; waiting for the tile's whole GROUP rather than for its own 128 rows makes
+          // every CTA enter a group at about the same time, as CTAs that start together do: the
+          // tiles in flight then share one group's rows and weights in L2 instead of two groups'.
+          if (p.disp.arrive != nullptr && t.rows > 0 && t.g >= groups_ready) {
+#ifdef MEP_GEMM_EXPERIMENTS
+            const unsigned long long t_begin = globaltimer_ns();
+#endif
+            unsigned long long t0 = 0ull;
+            unsigned spins = 0;
+            while ((groups_ready = *(volatile int*)&s_groups_ready) <= t.g) {
+              if ((++spins & 63u) == 0) {
+                if (t0 == 0ull) t0 = globaltimer_ns();
+                if (*abortp || globaltimer_ns() - t0 > p.timeout_ns) { ok = false; break; }
+              }
+            }
+            if (!ok) break;
+            __threadfence_block();
             fence_proxy_async();   // the rows were written through the async proxy (or by plain stores)
+#ifdef MEP_GEMM_EXPERIMENTS
+            if (p.status != nullptr)                   // experiments: total arrival wait of all CTAs, in microseconds
+              atomicAdd(p.status + 6, (int)((globaltimer_ns() - t_begin) / 1000ull));
+#endif
           }
         }
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
@@ -408,6 +437,22 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           }
         }
       }
+    } else if (DISP && p.disp.arrive != nullptr) {
+      // ---- arrival watchers (lanes 1..31): group after group, wait until every 128-row block of
+      // the group has all its rows, then publish the number of complete groups to lane 0 --------
+      if constexpr (DISP) {
+        for (int g = 0; g < p.ngroups; ++g) {
+          const int b0 = (g == 0 ? 0 : s_end[g - 1]) >> 7, b1 = s_end[g] >> 7;
+          bool okw = true;
+          for (int b = b0 + lane - 1; b < b1 && okw; b += 31)
+            okw = arrive_wait(p.disp.arrive + b, p.disp.expect, b, abortp, p);
+          if (!__all_sync(0xfffffffeu, okw)) break;
+          if (lane == 1) {
+            __threadfence_block();
+            *(volatile int*)&s_groups_ready = g + 1;
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ================= MMA issuer =================
@@ -456,9 +501,16 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     if constexpr (DISP) {
       if (p.disp.x != nullptr) {
         uint8_t* ring = tiles + (size_t)GEMM_STAGES * STAGE_BYTES;
+#ifdef MEP_GEMM_EXPERIMENTS
+        const unsigned long long t_begin = globaltimer_ns();
+#endif
         fused_dispatch_copy_warp<FD_NST>(
-            p.disp, ring, fd_full, fd_slots, (int)blockIdx.x, (int)gridDim.x,
+            p.disp, ring, fd_full, (int)blockIdx.x, (int)gridDim.x,
             [&](uint64_t* bar, uint32_t parity) { return gemm_wait(bar, parity, abortp, p, 7); });
+#ifdef MEP_GEMM_EXPERIMENTS
+        if (lane == 0 && p.status != nullptr)      // experiments: longest copy-warp run, in microseconds
+          atomicMax(p.status + 7, (int)((globaltimer_ns() - t_begin) / 1000ull));
+#endif
       }
     }
   } else {
@@ -1133,7 +1185,11 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       f.x = (const uint8_t*)d->disp_x; f.w = d->disp_w; f.dst = d->disp_dst; f.order = d->disp_order;
       f.zero_fill = d->disp_zero_fill;
     }
-    kp.timeout_ns = c.timeout_ns;      // waits on other ranks: the Buffer's budget, not the GEMM's
+    kp.arrive_timeout_ns = c.timeout_ns;                       // waits on other ranks: the Buffer's budget
+    kp.timeout_ns = c.timeout_ns + c.timeout_ns / 2 + 200000000ull;
+#ifdef MEP_GEMM_EXPERIMENTS
+    if (const char* e = getenv("MOONEP_B200_FD_EXPERIMENT")) f.debug = atoi(e);
+#endif
     if (d->epi == EPI_SWIGLU) {
       if (two) return launch_gemm2<false, true, EPI_SWIGLU, false, false, true>(kp, grid, stream);
       return launch_gemm<false, false, true, EPI_SWIGLU, false, true>(kp, grid, stream);

@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(PLAN_THREADS, 1) ep_plan_kernel(const PlanPara
   int32_t* scratch = p.scratch + (size_t)vr * p.scratch_ints;
   int32_t* hist_g = scratch + (size_t)4 * R * E;
   const int64_t tbl_off = p.tpe_off + (int64_t)parity * R * E;
+  pdl_launch_dependents();   // the dispatch kernel that follows may set itself up meanwhile
 
   // slice of entries owned by this CTA (whole tokens)
   const int tpc = (p.S + G - 1) / G;

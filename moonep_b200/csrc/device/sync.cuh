@@ -89,6 +89,17 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async;" ::: "memory");
 }
 
+// Programmatic dependent launch (reference: moonep/_common.py:393-406).  A kernel launched with
+// the programmatic-serialisation attribute may start while its predecessor on the stream still
+// runs; pdl_wait() blocks until the predecessor has COMPLETED and its writes are visible, so
+// everything before it (barrier set-up, shared-memory initialisation, parameter decoding) overlaps
+// the predecessor's tail.  pdl_launch_dependents() in the predecessor allows that early start.
+// Both are no-ops in kernels that are launched plainly.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ int32_t* sync_state_of(const SyncCtx& c) {
   return c.sync_state + (size_t)blockIdx.y * SYNC_STATE_INTS;
 }

@@ -46,6 +46,7 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
   c->plan_scratch = (int32_t*)plan_scratch;
   c->plan_scratch_ints = plan_scratch_ints(R, E, num_sms);
   c->timeout_ns = (unsigned long long)timeout_ns;
+  c->pdl = 0;
   int dev = 0;
   c->sm_count = 0;
   if (cudaGetDevice(&dev) == cudaSuccess)
@@ -54,6 +55,11 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
 }
 
 void mep_ctx_destroy(void* ctx) { delete (BufferCtx*)ctx; }
+
+// Programmatic dependent launch of the kernel chains (Buffer(enable_pdl=...)).
+void mep_ctx_set_pdl(void* ctx, int enable) {
+  if (ctx != nullptr) ((BufferCtx*)ctx)->pdl = enable ? 1 : 0;
+}
 
 // Registers the second symmetric row buffer (same geometry as the first).  Launchers select a
 // buffer with their `shard` argument; nothing in the context is switched around a launch.

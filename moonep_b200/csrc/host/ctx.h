@@ -31,6 +31,7 @@ struct BufferCtx {
   int64_t plan_scratch_ints;
   unsigned long long timeout_ns;
   int sm_count;
+  int pdl;                 // chain plan -> dispatch -> expand and prologue -> combine programmatically
 
   int Rv() const { return virt ? R : 1; }
   // Row buffer that a launch with the given shard index works on (null when it does not exist).
@@ -67,6 +68,34 @@ inline cudaError_t launch_coop(const void* kernel, dim3 grid, dim3 block, size_t
                                cudaStream_t stream, Params& params) {
   void* args[] = {(void*)&params};
   return cudaLaunchCooperativeKernel(kernel, grid, block, args, smem, stream);
+}
+
+// Launch of a kernel that FOLLOWS another kernel of the same chain on the stream.  With pdl != 0
+// (and outside stream capture) it carries the programmatic-serialisation attribute: the kernel
+// may be scheduled while its predecessor still runs and must call pdl_wait() before it touches
+// anything the predecessor wrote.  coop != 0 adds the cooperative attribute.
+template <class Params>
+inline cudaError_t launch_chained(const void* kernel, dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Params& params, int coop, int pdl) {
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (pdl && (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)) pdl = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (coop) { attr[n].id = cudaLaunchAttributeCooperative; attr[n].val.cooperative = 1; ++n; }
+  if (pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)n;
+  void* args[] = {(void*)&params};
+  return cudaLaunchKernelExC(&cfg, kernel, args);
 }
 
 // Same, but the CTAs are placed as clusters of two (x-neighbours share one TPC).  The copy kernels

@@ -148,10 +148,23 @@ int mep_vmm_supported(int device) {
   if (mep_device_attr(device, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR_SUPPORTED, &fd) != 0) return 0;
   return v && fd;
 }
+// Fabric handles are usable on this device: the attribute is set AND one granule can really be
+// created with that handle type (the attribute alone is also set on machines whose fabric
+// manager / IMEX channel is not configured, where creation fails).  Same probe as the reference
+// (csrc/nvl_shared_buffer.cuh:41-66).  Needs a current context on `device`.
 int mep_fabric_supported(int device) {
+  const Driver* d = drv();
+  if (!d) return 0;
   int v = 0;
-  if (mep_device_attr(device, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED, &v) != 0) return 0;
-  return v;
+  if (mep_device_attr(device, CU_DEVICE_ATTRIBUTE_HANDLE_TYPE_FABRIC_SUPPORTED, &v) != 0 || !v) return 0;
+  CUmemAllocationProp prop = chunk_prop(device, 1);
+  size_t g = 0;
+  if (d->MemGetAllocationGranularity(&g, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || g == 0)
+    return 0;
+  CUmemGenericAllocationHandle h;
+  if (d->MemCreate(&h, g, &prop, 0) != CUDA_SUCCESS) return 0;
+  d->MemRelease(h);
+  return 1;
 }
 int mep_multicast_supported(int device) {
   const Driver* d = drv();

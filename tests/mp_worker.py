@@ -203,7 +203,7 @@ def fused_dispatch_check(R, rank):
     assert buf.fused_dispatch_supported()
     pools = ExpertPools(R, E // R, H, Hp, buf.group, rank)
     bias = torch.zeros(E, device="cuda")
-    bias[: E // R] = 1.5                       # overload rank 0: redundant experts, prefetch slots
+    bias[: E // R] = 4.0                       # overload rank 0: redundant experts, prefetch slots
     g = torch.Generator(device="cuda").manual_seed(70 + rank)
     x = torch.randn(S, H, device="cuda", generator=g).bfloat16()
     dy = torch.randn(S, H, device="cuda", generator=g).bfloat16()
@@ -219,7 +219,7 @@ def fused_dispatch_check(R, rank):
             layer.sgd_step(0.05)
         buf.check()
         gemm.check_status()
-        used = int((layer.last_plan.experts_to_copy >= 0).sum())
+        used = max(used, int((layer.last_plan.experts_to_copy >= 0).sum()))
         res.append([y.detach().clone(), xo.grad.clone(), layer.w_gate.clone(), layer.w_up.clone(),
                     layer.w_down.clone(), layer.w_router.clone(), layer.last_plan.link.clone(),
                     layer.last_plan.src_info.clone()])
@@ -233,6 +233,53 @@ def fused_dispatch_check(R, rank):
     if rank == 0:
         print(f"fused dispatch R={R}: bit-identical over 3 steps, prefetch slots in use {int(tot) // R}", flush=True)
     buf.destroy()
+
+
+def symm_check(R, rank):
+    """Symmetric-memory utilities on real GPUs: the handle type the group agrees on, a tensor that
+    lives on one rank and is mapped by all, and (when this process runs with the NVLS overlay
+    switched on) a multicast store that lands in every rank's copy, with an orderly teardown."""
+    from moonep_b200 import buffer as symm
+    dev = torch.cuda.current_device()
+    kind = symm.handle_type_for_group(dist.group.WORLD, dev)
+    all_ok(kind in ("fd", "fabric"), "handle type", kind)
+    # ---- single-owner tensor: memory on the last rank, read and written by everyone -------------
+    owner = R - 1
+    t = symm.create_nvl_single_owner_tensor((4, 256), torch.int32, owner)
+    if rank == owner:
+        t.fill_(-1)
+    torch.cuda.synchronize(); dist.barrier()
+    t[rank % 4, rank * 8:(rank + 1) * 8] = rank + 100               # peer stores into the owner's memory
+    torch.cuda.synchronize(); dist.barrier()
+    want = torch.full((4, 256), -1, dtype=torch.int32, device="cuda")
+    for r in range(R):
+        want[r % 4, r * 8:(r + 1) * 8] = r + 100
+    all_ok(torch.equal(t, want), "single-owner tensor: every rank sees every rank's stores")
+    torch.cuda.synchronize(); dist.barrier()
+    symm.release(t)
+    # ---- NVLS overlay -------------------------------------------------------------------------------
+    n = 1024
+    tab, alias = symm.create_nvl_dist_multicast_tensor((R * n,), torch.int32)
+    rows = tab.shape[0] // R
+    if os.environ.get("MOONEP_B200_NVLS") == "1" and kind == "fd" and \
+            symm.nat.call("mep_multicast_supported", dev):
+        all_ok(alias is not None, "NVLS overlay was requested and is supported but was not built")
+    if alias is not None:
+        tab[rank * rows:(rank + 1) * rows].zero_()
+        torch.cuda.synchronize(); dist.barrier()
+        src = (torch.arange(n, device="cuda", dtype=torch.int32) + 1000 * (rank + 1))
+        symm.multimem_broadcast(alias, src, offset=rank * n)       # my row into everyone's table
+        torch.cuda.synchronize(); dist.barrier()
+        mine = tab[rank * rows: rank * rows + R * n].view(R, n)
+        want = torch.stack([torch.arange(n, device="cuda", dtype=torch.int32) + 1000 * (r + 1) for r in range(R)])
+        all_ok(torch.equal(mine, want), "multimem.st broadcast: my copy holds every rank's row")
+        torch.cuda.synchronize(); dist.barrier()
+        symm.release(alias)                  # the multicast mapping goes first, then the memory
+    dist.barrier()
+    symm.release(tab)
+    if rank == 0:
+        print(f"symm R={R}: handle type {kind}, single-owner ok, NVLS overlay {'ok' if alias is not None else 'not built'}",
+              flush=True)
 
 
 def decoder_check(R, rank):
@@ -343,6 +390,8 @@ def main():
         comm_checks(R, rank)
     if what in ("all", "layer"):
         layer_check(R, rank)
+    if what in ("all", "symm", "nvls"):
+        symm_check(R, rank)
     if what in ("all", "fused"):
         fused_dispatch_check(R, rank)
     if what in ("all", "decoder"):

@@ -11,8 +11,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(n, what, port):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MOONEP_B200_NVLS="0")
+def _run(n, what, port, nvls="0"):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MOONEP_B200_NVLS=nvls)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "mp_worker.py"), what]
@@ -21,9 +21,16 @@ def _run(n, what, port):
         f"worker failed:\n{res.stdout[-3000:]}\n{res.stderr[-3000:]}"
 
 
-@pytest.mark.parametrize("what,port", [("comm", 29611), ("layer", 29612), ("fused", 29617), ("decoder", 29615), ("leave", 29616)])
+@pytest.mark.parametrize("what,port", [("comm", 29611), ("symm", 29619), ("layer", 29612), ("fused", 29617), ("decoder", 29615), ("leave", 29616)])
 def test_two_gpus(what, port):
     _run(2, what, port)
+
+
+def test_two_gpus_nvls_overlay():
+    """The NVSwitch multicast overlay: create, add, bind, map, a multimem.st broadcast that every
+    rank reads back from its own copy, orderly teardown.  The only test that binds memory to a
+    multicast object; no rank leaves while it is bound."""
+    _run(2, "nvls", 29618, nvls="1")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")

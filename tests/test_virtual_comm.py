@@ -193,3 +193,31 @@ def test_bounded_wait_reports_status_and_recovers():
     out, _, _ = buf.combine(plan, h)
     buf.check()
     assert torch.equal(out.float(), (x.float() * 2).bfloat16().float())
+
+
+@pytest.mark.parametrize("R", [2, 4])
+def test_programmatic_dependent_launch_gives_identical_results(R):
+    """``enable_pdl`` only changes WHEN the follower kernels of a chain are scheduled (plan ->
+    dispatch -> expansion, pre-reduction -> combine); rows, weights, plan and sums are the same."""
+    from moonep_b200 import Buffer
+    from moonep_b200.utils.routing import routing_for_maxvio, tokens_per_expert
+    S, H, K, E, tp = 128, 256, 4, 8 * R, 16
+    topk, w, _, _ = routing_for_maxvio(S, K, E, R, 2.0, seed=3)
+    tpe = torch.stack([tokens_per_expert(topk[r], E) for r in range(R)]).cuda()
+    x = torch.randn(R, S, H, generator=torch.Generator().manual_seed(8)).bfloat16().cuda()
+    res = []
+    for pdl in (False, True):
+        buf = Buffer(S, H, K, E, R, num_sms=4, token_padding=tp, virtual=True, timeout_s=5.0, enable_pdl=pdl)
+        for _ in range(3):                                    # back to back: chains overlap their tails
+            hidden, w_nvs, cu, plan = buf.dispatch(x, w.cuda(), topk.cuda(), tpe)
+            y = (hidden.float() * w_nvs[:, :, None]).bfloat16()
+            out, w_back, _ = buf.combine(plan, y, w_nvs)
+        buf.check()
+        rows = cu[:, -1].tolist()
+        res.append((out.clone(), w_back.clone(), plan.dst.clone(), cu.clone(),
+                    [hidden[r, :rows[r]].clone() for r in range(R)]))
+        buf.destroy()
+    a, b = res
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+    for u, v in zip(a[4], b[4]):
+        assert torch.equal(u, v)
