@@ -29,6 +29,7 @@ dup_group_count, zero_pad_rows.  ``--sweep`` adds H in {3584, 7168} x K in {8, 1
 """
 import argparse
 import csv
+import datetime
 import json
 import os
 import sys
@@ -75,6 +76,7 @@ def routing_for_maxvio(S, K, E, R, target, seed=7):
 # ---- the two arms ---------------------------------------------------------------------------------
 class OursArm:
     name = "ours"
+    overlap_ok = True     # prefetch_weight / reduce_grad have their own barrier channel
 
     def __init__(self, S, H, Hp, K, E, R, rank, dev, num_sms, with_weights):
         sys.path.insert(0, ROOT)
@@ -168,6 +170,12 @@ class OursArm:
 
 class ReferenceArm:
     name = "reference"
+    # The reference's ops share one set of barrier words, so an asynchronous prefetch_weight may
+    # only overlap COMPUTE on the main stream: issued next to a combine on the main stream it
+    # stopped answering on this box (both kernels wait in the same cross-rank barrier).  The
+    # overlapped round trip is therefore not measured for this arm.
+    overlap_ok = False
+    overlap_note = "not run: the reference's async prefetch_weight next to a main-stream combine hangs (shared barrier words)"
 
     def __init__(self, S, H, Hp, K, E, R, rank, dev, num_sms, with_weights):
         ref_dir = os.path.join(ROOT, "baseline", "_ref")
@@ -261,7 +269,12 @@ def run_shape(args, arm_cls, S, H, Hp, K, E, R, rank, dev, rows_out):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(tm)
         timed.mean = round(float(tm) / R, 1)
+        if rank == 0:      # progress line: a later failure must not lose what was measured
+            print(f"[{arm.name}] op {timed.n}: {float(t):.1f} us", file=sys.stderr, flush=True)
+        timed.n += 1
         return round(float(t), 1)
+
+    timed.n = 0
 
     for target in [float(v) for v in args.maxvio.split(",")]:
         topk_all, w_all, mv = routing_for_maxvio(S, K, E, R, target)
@@ -289,7 +302,11 @@ def run_shape(args, arm_cls, S, H, Hp, K, E, R, rank, dev, rows_out):
                 arm.combine_fwd()
                 torch.cuda.current_stream().wait_event(ev)
 
-            row["roundtrip_overlapped_us"] = timed(overlapped)
+            if arm.overlap_ok:
+                row["roundtrip_overlapped_us"] = timed(overlapped)
+            else:
+                row["roundtrip_overlapped_us"] = None
+                row["roundtrip_overlapped_note"] = arm.overlap_note
         else:
             row["roundtrip_serial_us"] = timed(lambda: (arm.dispatch_fwd(), arm.combine_fwd()))
         row.update(arm.kernels(timed))
@@ -333,13 +350,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--sweep", action="store_true", help="H in {3584, 7168} x K in {8, 16} instead of one shape")
     ap.add_argument("--no-weights", action="store_true", help="skip prefetch / reduce_grad pools")
+    ap.add_argument("--nccl-timeout", type=int, default=120, help="seconds before a stuck collective ends the run")
     ap.add_argument("--out", default="", help="write all rows as JSON")
     ap.add_argument("--csv", default="", help="write all rows as CSV")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    # a short collective timeout: a hang in either arm ends the run in minutes, not in ten
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=args.nccl_timeout))
     R, rank = dist.get_world_size(), dist.get_rank()
     arm_cls = OursArm if args.impl == "ours" else ReferenceArm
     shapes = [(h, k) for h in (3584, 7168) for k in (8, 16)] if args.sweep else [(args.H, args.K)]

@@ -54,6 +54,28 @@ def main():
             torch.cuda.synchronize()
             ts.append(s.elapsed_time(e) * 1e3)
         res[name + "_us"] = round(min(ts[1:]), 1)
+    # the two local duplicate kernels on their own (bytes: rows read + rows written, all ranks)
+    from moonep_b200 import _native as nat
+    st = torch.cuda.current_stream().cuda_stream
+    link = plan.link
+    n_dup = int(((link & 0x40000000) != 0).sum())
+    n_prim = int((((link & 0x40000000) == 0) & ((link & 0x00FFFFFF) != 0x00FFFFFF)).sum())
+    for name, call, nbytes in (
+            ("k_expand", lambda: nat.call("mep_launch_expand", buf._ctx, plan.link.data_ptr(),
+                                          plan.cu_seqlens.data_ptr(), 0, st), (n_prim + n_dup) * a.H * 2),
+            ("k_prologue", lambda: nat.call("mep_launch_combine_prologue", buf._ctx, plan.link.data_ptr(),
+                                            plan.cu_seqlens.data_ptr(), st), (2 * n_prim + n_dup) * a.H * 2)):
+        ts = []
+        for _ in range(a.iters + 2):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            call()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e) * 1e3)
+        res[name + "_us"] = round(min(ts[1:]), 1)
+        res[name + "_gbs"] = round(nbytes / min(ts[1:]) / 1e3, 1)
+    res["dup_groups"], res["dup_rows"] = n_prim, n_dup
     buf.check()
     res.update(R=a.R, S=a.S, H=a.H, K=a.K, E=a.E, maxvio=round(mv, 2), rows_per_rank=int(plan.cu_seqlens[0, -1]))
     print(json.dumps(res))

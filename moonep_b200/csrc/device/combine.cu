@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 
 #include "common/layout.h"
+#include "device/dup_groups.cuh"
 #include "device/sync.cuh"
 #include "device/tma.cuh"
 #include "host/ctx.h"
@@ -38,6 +39,7 @@ __device__ __forceinline__ uint4 f32_to_bf16x8(const float* f) {
 
 // ---- prologue: primary += duplicates (local) ---------------------------------------------
 struct PrologueParams {
+  SyncCtx sync;               // status block and time budget of the bounded waits
   int H, epn;
   int64_t NvS, hidden_stride;
   int rank_base;
@@ -46,68 +48,114 @@ struct PrologueParams {
   const int32_t* cu_seqlens;  // [Rv][2epn]
 };
 
-constexpr int PROLOGUE_THREADS = 256;
+constexpr int PROLOGUE_ACC_THREADS = 128;
+constexpr int PROLOGUE_THREADS = 32 + PROLOGUE_ACC_THREADS;     // loader warp + 4 accumulator warps
 
-__global__ void __launch_bounds__(PROLOGUE_THREADS) ep_combine_prologue_kernel(const PrologueParams p) {
-  __shared__ int chain[PROLOGUE_THREADS / 32][MAX_TOPK];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ void named_bar_sync(int id, int n) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
+}
+
+// One CTA per SM.  CTA c owns a contiguous slice of this rank's rows; pass by pass it collects the
+// duplicate groups whose primary lies in the slice (dup_groups.cuh), then the loader lane streams
+// every group's rows (primary first, duplicates in chain order) through a ring of bulk loads while
+// four warps accumulate them in fp32 registers, round once to bf16 and hand the row to a bulk
+// store back onto the primary.  NV: 16-byte vectors per accumulator thread.
+template <int ST, int NV>
+__global__ void __launch_bounds__(PROLOGUE_THREADS, 1) ep_combine_prologue_kernel(const PrologueParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full[ST];
+  __shared__ __align__(8) uint64_t empty[ST];
+  __shared__ int last_flag[ST];
+  __shared__ DupGroupList L;
+  const SyncCtx& sc = p.sync;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vr = blockIdx.y, rank = p.rank_base + vr;
   const int32_t* link = p.link + (size_t)vr * p.NvS;
-  pdl_launch_dependents();   // the pull kernel may set up its ring; it waits for this kernel to end
-  int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
-  if (rows > p.NvS) rows = p.NvS;
-  uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
+  const uint32_t row_bytes = (uint32_t)p.H * 2u;
   const int nvec = p.H / 8;
-  const int64_t nwarps = (int64_t)gridDim.x * (PROLOGUE_THREADS / 32);
-  for (int64_t r = (int64_t)blockIdx.x * (PROLOGUE_THREADS / 32) + warp; r < rows; r += nwarps) {
-    int l = link[r];
-    if ((l & LINK_DUP_BIT) != 0) continue;
-    int next = l & LINK_NEXT_MASK;
-    if (next == LINK_NONE) continue;
-    int n = 0;
-    if (lane == 0) {
-      while (next != LINK_NONE && next < rows && n < MAX_TOPK - 1) {
-        chain[warp][n++] = next;
-        next = link[next] & LINK_NEXT_MASK;
-      }
-    }
-    n = __shfl_sync(0xffffffffu, n, 0);
-    __syncwarp();
-    uint4* prim = shard + (size_t)r * nvec;
-    // four independent 16-byte columns per lane and pass: (1 + n) * 4 loads in flight
-    for (int v0 = lane; v0 < nvec; v0 += 128) {
-      float acc[4][8];
-      uint4 raw[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int v = v0 + 32 * u;
-        raw[u] = v < nvec ? prim[v] : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) bf16x8_to_f32(raw[u], acc[u]);
-      for (int i = 0; i < n; ++i) {
-        const uint4* drow = shard + (size_t)chain[warp][i] * nvec;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = v0 + 32 * u;
-          raw[u] = v < nvec ? drow[v] : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float t[8];
-          bf16x8_to_f32(raw[u], t);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) acc[u][q] += t[q];
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int v = v0 + 32 * u;
-        if (v < nvec) prim[v] = f32_to_bf16x8(acc[u]);
-      }
-    }
-    __syncwarp();
+  uint8_t* ring = smem_raw;
+  uint8_t* out_stage = smem_raw + (size_t)ST * row_bytes;
+  if (tid == 0) {
+    for (int s = 0; s < ST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], PROLOGUE_ACC_THREADS / 32); }
+    mbar_fence_init();
   }
+  __syncthreads();
+  pdl_launch_dependents();   // the pull kernel may set up its ring; it waits for this kernel to end
+  int64_t rows64 = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
+  if (rows64 > p.NvS) rows64 = p.NvS;
+  const int rows = (int)rows64;
+  uint8_t* shard = reinterpret_cast<uint8_t*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
+  const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int s0 = min(rows, (int)blockIdx.x * per), s1 = min(rows, s0 + per);
+  uint32_t moved = 0;        // rows through the ring so far (loader and accumulators count alike)
+  uint32_t out_n = 0;        // rows stored so far (accumulators)
+  const int ta = tid - 32;
+  for (int r0 = s0; r0 < s1; r0 += DG_CHUNK) {
+    collect_dup_groups(L, link, r0, min(s1, r0 + DG_CHUNK), rows);
+    const int ng = L.n;
+    if (warp == 0) {
+      if (lane == 0) {
+        for (int j = 0; j < ng; ++j) {
+          const int n = L.count[j];
+          for (int e = 0; e <= n; ++e, ++moved) {
+            const int s = (int)(moved % ST);
+            if (moved >= ST) mbar_wait(sc, &empty[s], ((moved / ST) & 1u) ^ 1u, 20);
+            int r = e == 0 ? L.prim[j] : dup_row(L, link, j, e - 1);
+            if (r < 0 || r >= rows) { report_failure(sc, ST_BAD_INDEX, 21, j, r, rows); r = L.prim[j]; }
+            last_flag[s] = e == n;
+            mbar_expect_tx(&full[s], row_bytes);
+            bulk_g2s(ring + (size_t)s * row_bytes, shard + (size_t)r * row_bytes, row_bytes, &full[s]);
+          }
+        }
+      }
+      __syncwarp();
+    } else {
+      for (int j = 0; j < ng; ++j) {
+        float acc[NV][8];
+        bool first = true;
+        for (int guard = 0; guard < MAX_TOPK; ++guard, ++moved) {
+          const int s = (int)(moved % ST);
+          const bool ok = mbar_wait(sc, &full[s], (moved / ST) & 1u, 30);
+          const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
+          const int is_last = ok ? last_flag[s] : 1;
+#pragma unroll
+          for (int i = 0; i < NV; ++i) {
+            const int v = ta + i * PROLOGUE_ACC_THREADS;
+            if (v < nvec) {
+              float t[8];
+              bf16x8_to_f32(src[v], t);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) acc[i][q] = first ? t[q] : acc[i][q] + t[q];
+            }
+          }
+          first = false;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[s]);
+          if (is_last) { ++moved; break; }
+        }
+        // stage the bf16 row and hand it to one bulk store onto the primary
+        uint8_t* os = out_stage + (size_t)(out_n & 1u) * row_bytes;
+        if (out_n >= 2) {
+          if (ta == 0) bulk_wait_read<1>();
+          named_bar_sync(1, PROLOGUE_ACC_THREADS);
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+          const int v = ta + i * PROLOGUE_ACC_THREADS;
+          if (v < nvec) reinterpret_cast<uint4*>(os)[v] = f32_to_bf16x8(acc[i]);
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1, PROLOGUE_ACC_THREADS);
+        if (ta == 0) {
+          bulk_s2g(shard + (size_t)L.prim[j] * row_bytes, os, row_bytes);
+          bulk_commit();
+        }
+        ++out_n;
+      }
+    }
+    __syncthreads();         // the list is rebuilt by all threads in the next pass
+  }
+  if (ta == 0) bulk_wait<0>();
 }
 
 // ---- combine: remote pull + K-way fp32 sum -----------------------------------------------
@@ -123,10 +171,6 @@ struct CombineParams {
 
 constexpr int COMBINE_ACC_THREADS = 128;
 constexpr int COMBINE_THREADS = 32 + COMBINE_ACC_THREADS + 32;  // loader, 4 acc warps, weights
-
-__device__ __forceinline__ void named_bar_sync(int id, int n) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
-}
 
 // NV: 16-byte vectors per accumulator thread (H <= NV * 128 * 8)
 template <int ST, int NV>
@@ -344,6 +388,32 @@ static int launch_combine_nv(const BufferCtx& c, CombineParams& p, cudaStream_t 
   return fail(-2, "combine: H=%d does not fit a 2-stage ring", c.H);
 }
 
+template <int ST, int NV>
+static int launch_prologue_t(const BufferCtx& c, PrologueParams& p, size_t smem, cudaStream_t stream) {
+  static thread_local size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_combine_prologue_kernel<ST, NV>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  // one CTA per SM (a virtual group shares the SMs between its ranks)
+  int gx = c.num_sms_local / c.Rv();
+  if (gx < 1) gx = 1;
+  ep_combine_prologue_kernel<ST, NV><<<dim3(gx, c.Rv()), PROLOGUE_THREADS, smem, stream>>>(p);
+  MEP_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int NV>
+static int launch_prologue_nv(const BufferCtx& c, PrologueParams& p, cudaStream_t stream) {
+  const size_t row = (size_t)c.H * 2;
+  const size_t budget = 200 * 1024;
+  if (12 * row <= budget) return launch_prologue_t<10, NV>(c, p, 12 * row, stream);
+  if (6 * row <= budget) return launch_prologue_t<4, NV>(c, p, 6 * row, stream);
+  if (4 * row <= budget) return launch_prologue_t<2, NV>(c, p, 4 * row, stream);
+  return fail(-2, "combine prologue: H=%d does not fit a 2-stage ring", c.H);
+}
+
 }  // namespace mep
 
 using namespace mep;
@@ -354,14 +424,18 @@ int mep_launch_combine_prologue(const void* ctx_, const int32_t* link, const int
                                 cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   PrologueParams p;
+  p.sync = c.sync(KID_PROLOGUE);
   p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
   p.rank_base = c.virt ? 0 : c.rank;
   p.hidden = (__nv_bfloat16*)c.hidden; p.link = link; p.cu_seqlens = cu_seqlens;
-  // latency-bound row walks: several CTAs per SM keep enough loads in flight
-  dim3 grid(c.num_sms_local * 6, c.Rv());
-  ep_combine_prologue_kernel<<<grid, PROLOGUE_THREADS, 0, stream>>>(p);
-  MEP_CUDA_OK(cudaGetLastError());
-  return 0;
+  const int nvec = c.H / 8;
+  const int nv = (nvec + PROLOGUE_ACC_THREADS - 1) / PROLOGUE_ACC_THREADS;
+  if (nv <= 1) return launch_prologue_nv<1>(c, p, stream);
+  if (nv <= 2) return launch_prologue_nv<2>(c, p, stream);
+  if (nv <= 4) return launch_prologue_nv<4>(c, p, stream);
+  if (nv <= 7) return launch_prologue_nv<7>(c, p, stream);
+  if (nv <= 16) return launch_prologue_nv<16>(c, p, stream);
+  return fail(-3, "combine prologue: H=%d is larger than 16384", c.H);
 }
 
 // Finish a pushed combine: push [R][push_stride] bf16 rows / wpush [R][wpush_stride] fp32 scalars

@@ -15,6 +15,7 @@
 #include <cuda_runtime.h>
 
 #include "common/layout.h"
+#include "device/dup_groups.cuh"
 #include "device/sync.cuh"
 #include "device/tma.cuh"
 #include "host/ctx.h"
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
 
 // ---- duplicate expansion (local) ---------------------------------------------------------
 struct ExpandParams {
+  SyncCtx sync;                // status block and time budget of the bounded waits
   int H, epn;
   int64_t NvS, hidden_stride;
   int rank_base;
@@ -175,34 +177,81 @@ struct ExpandParams {
   const int32_t* cu_seqlens;   // [Rv][2epn]
 };
 
-constexpr int EXPAND_THREADS = 256;
+constexpr int EXPAND_THREADS = 128;
 
-__global__ void __launch_bounds__(EXPAND_THREADS) ep_expand_kernel(const ExpandParams p) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// One CTA per SM.  CTA c owns a contiguous slice of this rank's rows; pass by pass it collects the
+// duplicate groups whose primary lies in the slice (dup_groups.cuh) and then streams them: one
+// bulk load of the primary row into a ring stage, one bulk store per duplicate from that stage
+// (the duplicates of a group are issued by as many lanes in parallel), loads running ST/2 stages
+// ahead of the stores.  The rows never pass through registers.
+template <int ST>
+__global__ void __launch_bounds__(EXPAND_THREADS, 1) ep_expand_kernel(const ExpandParams p) {
+  constexpr int LA = ST / 2;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full[ST];
+  __shared__ DupGroupList L;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vr = blockIdx.y, rank = p.rank_base + vr;
   const int32_t* link = p.link + (size_t)vr * p.NvS;
-  pdl_wait();                // the dispatch kernel before this one has completed
-  int64_t rows = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
-  if (rows > p.NvS) rows = p.NvS;
-  uint4* shard = reinterpret_cast<uint4*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
-  const int nvec = p.H / 8;
-  const int64_t nwarps = (int64_t)gridDim.x * (EXPAND_THREADS / 32);
-  for (int64_t r = (int64_t)blockIdx.x * (EXPAND_THREADS / 32) + warp; r < rows; r += nwarps) {
-    int l = link[r];
-    if ((l & LINK_DUP_BIT) != 0) continue;
-    int next = l & LINK_NEXT_MASK;
-    const uint4* src = shard + (size_t)r * nvec;
-    for (int hop = 0; next != LINK_NONE && next < rows && hop < MAX_TOPK; ++hop) {
-      uint4* dstp = shard + (size_t)next * nvec;
-      int v = lane;
-      for (; v + 96 < nvec; v += 128) {
-        uint4 a = src[v], b = src[v + 32], c2 = src[v + 64], d = src[v + 96];
-        dstp[v] = a; dstp[v + 32] = b; dstp[v + 64] = c2; dstp[v + 96] = d;
-      }
-      for (; v < nvec; v += 32) dstp[v] = src[v];
-      next = link[next] & LINK_NEXT_MASK;
-    }
+  const uint32_t row_bytes = (uint32_t)p.H * 2u;
+  uint8_t* ring = smem_raw;
+  if (tid == 0) {
+    for (int s = 0; s < ST; ++s) mbar_init(&full[s], 1);
+    mbar_fence_init();
   }
+  __syncthreads();
+  pdl_wait();                // the dispatch kernel before this one has completed
+  int64_t rows64 = p.cu_seqlens[(size_t)vr * 2 * p.epn + 2 * p.epn - 1];
+  if (rows64 > p.NvS) rows64 = p.NvS;
+  const int rows = (int)rows64;
+  uint8_t* shard = reinterpret_cast<uint8_t*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
+  const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int s0 = min(rows, (int)blockIdx.x * per), s1 = min(rows, s0 + per);
+  uint32_t issued = 0;       // groups this CTA has pushed through the ring so far (all passes)
+  for (int r0 = s0; r0 < s1; r0 += DG_CHUNK) {
+    collect_dup_groups(L, link, r0, min(s1, r0 + DG_CHUNK), rows);
+    const int ng = L.n;
+    if (warp == 0 && ng > 0) {
+      if (lane == 0) {
+        for (int j = 0; j < LA && j < ng; ++j) {
+          const uint32_t q = issued + j;
+          mbar_expect_tx(&full[q % ST], row_bytes);
+          bulk_g2s(ring + (size_t)(q % ST) * row_bytes, shard + (size_t)L.prim[j] * row_bytes, row_bytes,
+                   &full[q % ST]);
+        }
+      }
+      __syncwarp();
+      for (int j = 0; j < ng; ++j) {
+        const uint32_t q = issued + j;
+        const int s = (int)(q % ST);
+        mbar_wait(p.sync, &full[s], (q / ST) & 1u, 10);
+        const int n = L.count[j];
+        if (lane < n) {
+          const int dr = dup_row(L, link, j, lane);
+          if (dr >= 0 && dr < rows)
+            bulk_s2g(shard + (size_t)dr * row_bytes, ring + (size_t)s * row_bytes, row_bytes);
+        }
+        bulk_commit();
+        if (j + LA < ng) {
+          // the stage to refill was last read by the stores of group q + LA - ST
+          bulk_wait_read<ST - LA>();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t q2 = q + LA;
+            mbar_expect_tx(&full[q2 % ST], row_bytes);
+            bulk_g2s(ring + (size_t)(q2 % ST) * row_bytes, shard + (size_t)L.prim[j + LA] * row_bytes,
+                     row_bytes, &full[q2 % ST]);
+          }
+        }
+      }
+      // the next pass reuses the stages from the start: everything of this pass has left them
+      bulk_wait_read<0>();
+      __syncwarp();
+    }
+    issued += (uint32_t)ng;
+    __syncthreads();         // the list is rebuilt by all threads in the next pass
+  }
+  if (warp == 0) bulk_wait<0>();
 }
 
 // ---- fused dispatch -> GEMM path: the two small kernels around the fused GEMM launches ----------
@@ -295,13 +344,29 @@ int mep_launch_expand(const void* ctx_, const int32_t* link, const int32_t* cu_s
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (c.shard_base(shard) == nullptr) return fail(-4, "expand: shard %d does not exist", shard);
   ExpandParams p;
+  p.sync = c.sync(KID_EXPAND);
   p.H = c.H; p.epn = c.epn; p.NvS = c.NvS; p.hidden_stride = c.hidden_stride;
   p.rank_base = c.virt ? 0 : c.rank;
   p.hidden = (__nv_bfloat16*)c.shard_base(shard); p.link = link; p.cu_seqlens = cu_seqlens;
-  // latency-bound row walks: several CTAs per SM keep enough loads in flight
-  dim3 grid(c.num_sms_local * 6, c.Rv());
-  MEP_CUDA_OK(launch_chained((const void*)ep_expand_kernel, grid, dim3(EXPAND_THREADS), 0, stream, p,
-                             /*coop=*/0, c.pdl));
+  // one CTA per SM (a virtual group shares the SMs between its ranks); the ring takes what
+  // shared memory the group lists leave
+  const size_t row = (size_t)c.H * 2;
+  int gx = c.num_sms_local / c.Rv();
+  if (gx < 1) gx = 1;
+  dim3 grid(gx, c.Rv());
+  const void* kern;
+  size_t smem;
+  if (8 * row <= 160 * 1024) { kern = (const void*)ep_expand_kernel<8>; smem = 8 * row; }
+  else if (4 * row <= 200 * 1024) { kern = (const void*)ep_expand_kernel<4>; smem = 4 * row; }
+  else if (2 * row <= 200 * 1024) { kern = (const void*)ep_expand_kernel<2>; smem = 2 * row; }
+  else return fail(-2, "expand: H=%d does not fit a 2-stage ring", c.H);
+  static thread_local size_t configured[3] = {0, 0, 0};
+  const int which = kern == (const void*)ep_expand_kernel<8> ? 0 : (kern == (const void*)ep_expand_kernel<4> ? 1 : 2);
+  if (smem > 48 * 1024 && smem > configured[which]) {
+    MEP_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[which] = smem;
+  }
+  MEP_CUDA_OK(launch_chained(kern, grid, dim3(EXPAND_THREADS), smem, stream, p, /*coop=*/0, c.pdl));
   return 0;
 }
 

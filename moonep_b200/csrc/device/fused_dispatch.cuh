@@ -11,9 +11,10 @@
 //
 // Arrival tracking.  Each rank owns one int32 counter per 128-row block of its row buffer (ARRIVE
 // in the meta chunk).  A sender adds the number of row parts it has completed to the destination
-// block's counter with red.release.sys after cp.async.bulk.wait_group has reported the copies
-// complete; the GEMM's TMA producer polls the counter of the block it is about to load with
-// ld.acquire.sys (bounded), then fences the async proxy and loads.  A block expects 128 rows x
+// block's counter (a system-scope reduction) after cp.async.bulk.wait_group has reported the
+// copies complete; watcher lanes of the GEMM's producer warp poll the counters of the group the
+// producer is about to load with ld.acquire.sys (bounded, with back-off), the producer then
+// fences the async proxy and loads.  A block expects 128 rows x
 // `nsplit` parts: real rows arrive from their source ranks, padding rows are zeroed by the
 // owner's own copy warps and counted the same way.  In this mode every (token, k) entry travels
 // as a real row: a duplicate of a token on one destination rank is not expanded locally, because
@@ -160,7 +161,15 @@ __device__ __forceinline__ void fused_dispatch_copy_warp(const FusedDispatch& d,
         }
       }
     }
-    __syncwarp();     // the weight stores above are ordered before the releases below
+    // The route weights above are plain stores to the peers; ONE system-scope fence per batch (by
+    // lane 0, made cumulative over the warp by the barriers around it) orders them before every
+    // arrival signal of this batch.  The rows themselves need no fence: a signal is only issued
+    // after cp.async.bulk.wait_group has reported the row's copy complete, so a relaxed reduction
+    // is enough per round.  (A release per round cost a full drain of the SM's stores each time
+    // and made the copy warp, not NVLink, the limit.)
+    __syncwarp();
+    if (lane == 0 && !fd_dbg(d, 1)) fence_sys();
+    __syncwarp();
     // ---- rounds of NST units: lane i < NST moves unit u0 + r0 + i through stage i ---------------
     for (int r0 = 0; r0 < PER_BATCH && u0 + r0 < n_units; r0 += NST) {
       const int from = r0 + (lane < NST ? lane : 0);
@@ -191,8 +200,7 @@ __device__ __forceinline__ void fused_dispatch_copy_warp(const FusedDispatch& d,
       const unsigned long long key = (act && sent) ? s_ctr : 0ull;
       const unsigned grp = __match_any_sync(0xffffffffu, key);
       if (key != 0ull && lane == __ffs(grp) - 1) {
-        if (fd_dbg(d, 1)) atomicAdd_system(reinterpret_cast<int*>(key), __popc(grp));
-        else red_release_sys_add(reinterpret_cast<int32_t*>(key), __popc(grp));
+        red_relaxed_sys_add(reinterpret_cast<int32_t*>(key), __popc(grp));
       }
       if (!ok) break;
     }

@@ -79,6 +79,9 @@ __device__ __forceinline__ void st_release_gpu(int32_t* p, int v) {
 __device__ __forceinline__ void red_release_sys_add(int32_t* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void red_relaxed_sys_add(int32_t* p, int v) {
+  asm volatile("red.relaxed.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_gpu_add(int32_t* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
