@@ -50,6 +50,9 @@ def parse():
     ap.add_argument("--no-fused-dispatch", action="store_true",
                     help="stand-alone dispatch kernels (all-to-all, barrier, duplicate expansion) before the "
                          "gate/up and down-dgrad GEMMs instead of the dispatch carried by those GEMM launches")
+    ap.add_argument("--ab-dispatch", action="store_true",
+                    help="also time the step with the other dispatch variant (fused into the GEMMs / stand-alone) "
+                         "in the same process, interleaved round by round, and report both under 'ab_dispatch'")
     ap.add_argument("--copy-dispatch-out", action="store_true",
                     help="forward dispatch copies its rows out of the shard (instead of keeping them in a "
                          "second shard until backward is done)")
@@ -269,6 +272,34 @@ def run_ours(args):
 
     ms_e2e = timed(e2e_step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    # ---- optional A/B of the dispatch variant under identical clocks ---------------------------
+    ab = None
+    if args.ab_dispatch and graphed:
+        from moonep_b200.utils.graph import GraphedStep
+        layer_b = MoELayer(buf, hp, pools, seed=0, fused_combine=not args.no_fused_combine,
+                           hidden_in_place=not args.copy_dispatch_out, fused_dispatch=not layer.fused_dispatch)
+        layer_b.router_bias = layer.router_bias
+        if not args.no_fused_sgd:
+            layer_b.fuse_sgd(args.lr)
+
+        def step_b_eager(x):
+            x = x.detach().requires_grad_(True)
+            loss = layer_b(x).float().pow(2).mean()
+            loss.backward()
+            layer_b.sgd_step(args.lr)
+            return loss
+
+        for i in range(3):
+            step_b_eager(xs[i % n_batches])
+        gs_b = GraphedStep(step_b_eager, [xs[0]], warmup=1)
+        best = {"a": 1e9, "b": 1e9}
+        for _ in range(3):
+            best["a"] = min(best["a"], timed(lambda i: step(xs[i % n_batches]), args.steps))
+            best["b"] = min(best["b"], timed(lambda i: gs_b(xs[i % n_batches]), args.steps))
+        name = lambda fused: "fused_into_gemm_ms" if fused else "standalone_ms"
+        ab = {name(layer.fused_dispatch): best["a"], name(layer_b.fused_dispatch): best["b"],
+              "what": "ms per step, best of 3 interleaved rounds, both variants in this process"}
+        buf.check()
     # ---- communication round trip at the same shape (plan + dispatch + prefetch + combine) -----
     topk_w = {}
 
@@ -319,6 +350,7 @@ def run_ours(args):
                 "h2d_bytes_per_step": s * h * 2, "d2h_bytes_per_step": 4,
                 "loss_last": losses[-1] if losses else None},
         "gpu_launches": launches,
+        "ab_dispatch": ab,
         "comm_roundtrip_us": ms_comm * 1e3,
         "comm_roundtrip_what": "plan + dispatch + prefetch_weight + combine, zero-copy, max over ranks",
         "peak_mem_gb": peak_gb,

@@ -186,7 +186,6 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
   const uint32_t row_bytes = (uint32_t)p.H * 2u;
   const int nvec = p.H / 8;
   uint8_t* ring = smem_raw;
-  uint8_t* out_stage = smem_raw + (size_t)ST * row_bytes;
 
   if (tid == 0) {
     for (int s = 0; s < ST; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], COMBINE_ACC_THREADS / 32); }
@@ -255,25 +254,17 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
         ++cons;
         if (is_last) break;
       }
-      // stage the bf16 row and hand it to one bulk store
-      uint8_t* os = out_stage + (size_t)(j & 1) * row_bytes;
-      if (j >= 2) {
-        if (ta == 0) bulk_wait_read<1>();
-        named_bar_sync(1, COMBINE_ACC_THREADS);
-      }
+      // The summed row goes straight from the accumulators to this rank's output with 16-byte
+      // stores (consecutive threads, consecutive vectors).  The output is local memory, so the
+      // stores cost little, and keeping them out of shared memory leaves two more stages to the
+      // ring of remote reads: the pull is bound by bytes in flight over the read latency.
+      uint4* orow = reinterpret_cast<uint4*>(out + (size_t)(c + (int64_t)j * G) * p.H);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         int v = ta + i * COMBINE_ACC_THREADS;
-        if (v < nvec) reinterpret_cast<uint4*>(os)[v] = f32_to_bf16x8(acc[i]);
-      }
-      fence_proxy_async_smem();
-      named_bar_sync(1, COMBINE_ACC_THREADS);
-      if (ta == 0) {
-        bulk_s2g(out + (size_t)(c + (int64_t)j * G) * p.H, os, row_bytes);
-        bulk_commit();
+        if (v < nvec) orow[v] = f32_to_bf16x8(acc[i]);
       }
     }
-    if (ta == 0) bulk_wait<0>();
   } else if (p.w_out != nullptr) {
     // ---- route weights back to token-major, raw 32-bit words -------------------------------
     float* w_out = p.w_out + (size_t)vr * p.N;
@@ -381,10 +372,10 @@ template <int NV>
 static int launch_combine_nv(const BufferCtx& c, CombineParams& p, cudaStream_t stream) {
   const size_t row = (size_t)c.H * 2;
   const size_t budget = c.virt ? 100 * 1024 : 210 * 1024;
-  if (14 * row <= budget) return launch_combine_t<12, NV>(c, p, 14 * row, stream);
-  if (10 * row <= budget) return launch_combine_t<8, NV>(c, p, 10 * row, stream);
-  if (6 * row <= budget) return launch_combine_t<4, NV>(c, p, 6 * row, stream);
-  if (4 * row <= 220 * 1024) return launch_combine_t<2, NV>(c, p, 4 * row, stream);
+  if (14 * row <= budget) return launch_combine_t<14, NV>(c, p, 14 * row, stream);
+  if (10 * row <= budget) return launch_combine_t<10, NV>(c, p, 10 * row, stream);
+  if (6 * row <= budget) return launch_combine_t<6, NV>(c, p, 6 * row, stream);
+  if (3 * row <= 220 * 1024) return launch_combine_t<3, NV>(c, p, 3 * row, stream);
   return fail(-2, "combine: H=%d does not fit a 2-stage ring", c.H);
 }
 

@@ -241,7 +241,8 @@ int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* co
     p.expert_elems[t] = expert_elems[t]; p.rank_stride[t] = rank_stride[t];
   }
   if (c.virt) return launch_gr_t<4>(c, p, stream);
-  return launch_gr_t<8>(c, p, stream);
+  // a pull is bound by bytes in flight over the remote read latency: take what shared memory allows
+  return launch_gr_t<13>(c, p, stream);
 }
 
 // Pure cross-rank barrier (one CTA per rank).

@@ -993,6 +993,19 @@ static int make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols
   return 0;
 }
 
+// Fused dispatch launches: CTAs of different ranks wait for one another's copy warps, so the whole
+// grid must be resident at once.  The grid never exceeds what the device holds next to the weight
+// ops' CTAs, and a cooperative launch makes the driver guarantee the residency; MOONEP_B200_FD_COOP=0
+// launches plainly instead (the waits stay bounded either way).
+static bool fused_dispatch_cooperative() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MOONEP_B200_FD_COOP");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
 // CTA-pair launch: clusters of two CTAs, one pair per two SMs.
 template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false, bool DISP = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
@@ -1017,7 +1030,7 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   attr[1].id = cudaLaunchAttributeCooperative;
   attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = DISP ? 2 : 1;
+  cfg.numAttrs = (DISP && fused_dispatch_cooperative()) ? 2 : 1;
   // A persistent grid must not exceed what is resident at once: not every SM can be paired
   // into a cluster (GPCs with an odd SM count leave one out), and a second wave of persistent
   // CTAs would double the run time.
@@ -1060,8 +1073,13 @@ static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (grid > sms) grid = sms;
-    GemmKParams kpc = kp;
-    MEP_CUDA_OK(launch_coop((const void*)kern, dim3(grid), dim3(GEMM_THREADS_DISP), GEMM_SMEM, stream, kpc));
+    if (fused_dispatch_cooperative()) {
+      GemmKParams kpc = kp;
+      MEP_CUDA_OK(launch_coop((const void*)kern, dim3(grid), dim3(GEMM_THREADS_DISP), GEMM_SMEM, stream, kpc));
+    } else {
+      kern<<<grid, GEMM_THREADS_DISP, GEMM_SMEM, stream>>>(kp);
+      MEP_CUDA_OK(cudaGetLastError());
+    }
     return 0;
   }
   kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(kp);
