@@ -37,6 +37,67 @@ __device__ __forceinline__ uint4 f32_to_bf16x8(const float* f) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ---- row accumulation in packed fp32 pairs ---------------------------------------------------
+// The kernels that sum bf16 rows in fp32 (pre-reduction, pull combine) are bound by instruction
+// issue, not by memory, when they run one accumulator warp per scheduler with scalar adds
+// (measured: ~220 warp instructions and 0.65 us per 14 KB row).  They therefore keep their
+// accumulators as f32x2 pairs (add.rn.f32x2, one instruction per two sums, same IEEE result per
+// lane as two scalar adds), take the first row of a sum by assignment, and use seven accumulator
+// warps, so that every scheduler has a second warp to issue from.
+constexpr int ACC_WARPS = 7;
+constexpr int ACC_THREADS = ACC_WARPS * 32;      // 224: a 7168-element row is exactly 4 vectors per thread
+
+__device__ __forceinline__ unsigned long long pack_f32x2(uint32_t lo, uint32_t hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 8 bf16 (one 16-byte vector) as four fp32 pairs
+__device__ __forceinline__ void bf16x8_to_f32x2(const uint4& v, unsigned long long* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) f[i] = pack_f32x2(w[i] << 16, w[i] & 0xFFFF0000u);
+}
+__device__ __forceinline__ uint4 f32x2_to_bf16x8(const unsigned long long* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(f[i]));
+    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(lo), __uint_as_float(hi));
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+// acc (+)= one staged row; `first` is uniform over the CTA's accumulator threads
+template <int NV>
+__device__ __forceinline__ void accumulate_row(unsigned long long (&acc)[NV][4], const uint4* src, int ta,
+                                               int nvec, bool first) {
+  if (first) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = ta + i * ACC_THREADS;
+      if (v < nvec) bf16x8_to_f32x2(src[v], acc[i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = ta + i * ACC_THREADS;
+      if (v < nvec) {
+        unsigned long long t[4];
+        bf16x8_to_f32x2(src[v], t);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) acc[i][q] = add_f32x2(acc[i][q], t[q]);
+      }
+    }
+  }
+}
+
 // ---- prologue: primary += duplicates (local) ---------------------------------------------
 struct PrologueParams {
   SyncCtx sync;               // status block and time budget of the bounded waits
@@ -48,8 +109,8 @@ struct PrologueParams {
   const int32_t* cu_seqlens;  // [Rv][2epn]
 };
 
-constexpr int PROLOGUE_ACC_THREADS = 128;
-constexpr int PROLOGUE_THREADS = 32 + PROLOGUE_ACC_THREADS;     // loader warp + 4 accumulator warps
+constexpr int PROLOGUE_ACC_THREADS = ACC_THREADS;
+constexpr int PROLOGUE_THREADS = 32 + PROLOGUE_ACC_THREADS;     // loader warp + accumulator warps
 
 __device__ __forceinline__ void named_bar_sync(int id, int n) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
@@ -58,7 +119,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int n) {
 // One CTA per SM.  CTA c owns a contiguous slice of this rank's rows; pass by pass it collects the
 // duplicate groups whose primary lies in the slice (dup_groups.cuh), then the loader lane streams
 // every group's rows (primary first, duplicates in chain order) through a ring of bulk loads while
-// four warps accumulate them in fp32 registers, round once to bf16 and hand the row to a bulk
+// the accumulator warps sum them in fp32 registers, round once to bf16 and hand the row to a bulk
 // store back onto the primary.  NV: 16-byte vectors per accumulator thread.
 template <int ST, int NV>
 __global__ void __launch_bounds__(PROLOGUE_THREADS, 1) ep_combine_prologue_kernel(const PrologueParams p) {
@@ -111,23 +172,14 @@ __global__ void __launch_bounds__(PROLOGUE_THREADS, 1) ep_combine_prologue_kerne
       __syncwarp();
     } else {
       for (int j = 0; j < ng; ++j) {
-        float acc[NV][8];
+        unsigned long long acc[NV][4];
         bool first = true;
         for (int guard = 0; guard < MAX_TOPK; ++guard, ++moved) {
           const int s = (int)(moved % ST);
           const bool ok = mbar_wait(sc, &full[s], (moved / ST) & 1u, 30);
           const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
           const int is_last = ok ? last_flag[s] : 1;
-#pragma unroll
-          for (int i = 0; i < NV; ++i) {
-            const int v = ta + i * PROLOGUE_ACC_THREADS;
-            if (v < nvec) {
-              float t[8];
-              bf16x8_to_f32(src[v], t);
-#pragma unroll
-              for (int q = 0; q < 8; ++q) acc[i][q] = first ? t[q] : acc[i][q] + t[q];
-            }
-          }
+          accumulate_row<NV>(acc, src, ta, nvec, first);
           first = false;
           __syncwarp();
           if (lane == 0) mbar_arrive(&empty[s]);
@@ -142,7 +194,7 @@ __global__ void __launch_bounds__(PROLOGUE_THREADS, 1) ep_combine_prologue_kerne
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
           const int v = ta + i * PROLOGUE_ACC_THREADS;
-          if (v < nvec) reinterpret_cast<uint4*>(os)[v] = f32_to_bf16x8(acc[i]);
+          if (v < nvec) reinterpret_cast<uint4*>(os)[v] = f32x2_to_bf16x8(acc[i]);
         }
         fence_proxy_async_smem();
         named_bar_sync(1, PROLOGUE_ACC_THREADS);
@@ -169,8 +221,8 @@ struct CombineParams {
   float* w_out;                  // [Rv][S][K] or null
 };
 
-constexpr int COMBINE_ACC_THREADS = 128;
-constexpr int COMBINE_THREADS = 32 + COMBINE_ACC_THREADS + 32;  // loader, 4 acc warps, weights
+constexpr int COMBINE_ACC_THREADS = ACC_THREADS;
+constexpr int COMBINE_THREADS = 32 + COMBINE_ACC_THREADS + 32;  // loader, accumulator warps, weights
 
 // NV: 16-byte vectors per accumulator thread (H <= NV * 128 * 8)
 template <int ST, int NV>
@@ -229,26 +281,15 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
     __nv_bfloat16* out = p.out + (size_t)vr * p.S * p.H;
     int cons = 0;
     for (int j = 0; j < n_tok; ++j) {
-      float acc[NV][8];
-#pragma unroll
-      for (int i = 0; i < NV; ++i)
-#pragma unroll
-        for (int q = 0; q < 8; ++q) acc[i][q] = 0.f;
+      unsigned long long acc[NV][4];
+      bool first = true;
       for (int guard = 0; guard < MAX_TOPK; ++guard) {
         const int s = cons % ST;
         bool ok = mbar_wait(sc, &full[s], (uint32_t)(cons / ST) & 1u, 30);
         const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
         const int is_last = ok ? last_flag[s] : 1;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-          int v = ta + i * COMBINE_ACC_THREADS;
-          if (v < nvec) {
-            float t[8];
-            bf16x8_to_f32(src[v], t);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[i][q] += t[q];
-          }
-        }
+        accumulate_row<NV>(acc, src, ta, nvec, first);
+        first = false;
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
         ++cons;
@@ -262,7 +303,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         int v = ta + i * COMBINE_ACC_THREADS;
-        if (v < nvec) orow[v] = f32_to_bf16x8(acc[i]);
+        if (v < nvec) orow[v] = f32x2_to_bf16x8(acc[i]);
       }
     }
   } else if (p.w_out != nullptr) {
@@ -424,8 +465,7 @@ int mep_launch_combine_prologue(const void* ctx_, const int32_t* link, const int
   if (nv <= 1) return launch_prologue_nv<1>(c, p, stream);
   if (nv <= 2) return launch_prologue_nv<2>(c, p, stream);
   if (nv <= 4) return launch_prologue_nv<4>(c, p, stream);
-  if (nv <= 7) return launch_prologue_nv<7>(c, p, stream);
-  if (nv <= 16) return launch_prologue_nv<16>(c, p, stream);
+  if (nv <= 10) return launch_prologue_nv<10>(c, p, stream);
   return fail(-3, "combine prologue: H=%d is larger than 16384", c.H);
 }
 
@@ -464,8 +504,7 @@ int mep_launch_combine(const void* ctx_, const int32_t* dst, void* out, float* w
   if (nv <= 1) return launch_combine_nv<1>(c, p, stream);
   if (nv <= 2) return launch_combine_nv<2>(c, p, stream);
   if (nv <= 4) return launch_combine_nv<4>(c, p, stream);
-  if (nv <= 7) return launch_combine_nv<7>(c, p, stream);
-  if (nv <= 16) return launch_combine_nv<16>(c, p, stream);
+  if (nv <= 10) return launch_combine_nv<10>(c, p, stream);
   return fail(-3, "combine: H=%d is larger than 16384", c.H);
 }
 
