@@ -116,8 +116,8 @@ __device__ __forceinline__ void named_bar_sync(int id, int n) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
 }
 
-// One CTA per SM.  CTA c owns a contiguous slice of this rank's rows; pass by pass it collects the
-// duplicate groups whose primary lies in the slice (dup_groups.cuh), then the loader lane streams
+// One CTA per SM.  Pass by pass a CTA collects the duplicate groups whose primary lies in its share
+// of this rank's rows (blocks of rows dealt round-robin, dup_groups.cuh), then the loader lane streams
 // every group's rows (primary first, duplicates in chain order) through a ring of bulk loads while
 // the accumulator warps sum them in fp32 registers, round once to bf16 and hand the row to a bulk
 // store back onto the primary.  NV: 16-byte vectors per accumulator thread.
@@ -146,13 +146,12 @@ __global__ void __launch_bounds__(PROLOGUE_THREADS, 1) ep_combine_prologue_kerne
   if (rows64 > p.NvS) rows64 = p.NvS;
   const int rows = (int)rows64;
   uint8_t* shard = reinterpret_cast<uint8_t*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
-  const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int s0 = min(rows, (int)blockIdx.x * per), s1 = min(rows, s0 + per);
+  const int n_pass = dup_group_passes(rows, (int)gridDim.x);
   uint32_t moved = 0;        // rows through the ring so far (loader and accumulators count alike)
   uint32_t out_n = 0;        // rows stored so far (accumulators)
   const int ta = tid - 32;
-  for (int r0 = s0; r0 < s1; r0 += DG_CHUNK) {
-    collect_dup_groups(L, link, r0, min(s1, r0 + DG_CHUNK), rows);
+  for (int pass = 0; pass < n_pass; ++pass) {
+    collect_dup_groups(L, link, pass, (int)blockIdx.x, (int)gridDim.x, rows);
     const int ng = L.n;
     if (warp == 0) {
       if (lane == 0) {

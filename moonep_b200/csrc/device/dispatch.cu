@@ -179,8 +179,8 @@ struct ExpandParams {
 
 constexpr int EXPAND_THREADS = 128;
 
-// One CTA per SM.  CTA c owns a contiguous slice of this rank's rows; pass by pass it collects the
-// duplicate groups whose primary lies in the slice (dup_groups.cuh) and then streams them: one
+// One CTA per SM.  Pass by pass a CTA collects the duplicate groups whose primary lies in its share
+// of this rank's rows (blocks of rows dealt round-robin, dup_groups.cuh) and then streams them: one
 // bulk load of the primary row into a ring stage, one bulk store per duplicate from that stage
 // (the duplicates of a group are issued by as many lanes in parallel), loads running ST/2 stages
 // ahead of the stores.  The rows never pass through registers.
@@ -205,11 +205,10 @@ __global__ void __launch_bounds__(EXPAND_THREADS, 1) ep_expand_kernel(const Expa
   if (rows64 > p.NvS) rows64 = p.NvS;
   const int rows = (int)rows64;
   uint8_t* shard = reinterpret_cast<uint8_t*>(p.hidden + (size_t)rank * p.hidden_stride * p.H);
-  const int per = (rows + (int)gridDim.x - 1) / (int)gridDim.x;
-  const int s0 = min(rows, (int)blockIdx.x * per), s1 = min(rows, s0 + per);
+  const int n_pass = dup_group_passes(rows, (int)gridDim.x);
   uint32_t issued = 0;       // groups this CTA has pushed through the ring so far (all passes)
-  for (int r0 = s0; r0 < s1; r0 += DG_CHUNK) {
-    collect_dup_groups(L, link, r0, min(s1, r0 + DG_CHUNK), rows);
+  for (int pass = 0; pass < n_pass; ++pass) {
+    collect_dup_groups(L, link, pass, (int)blockIdx.x, (int)gridDim.x, rows);
     const int ng = L.n;
     if (warp == 0 && ng > 0) {
       if (lane == 0) {

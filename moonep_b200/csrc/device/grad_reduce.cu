@@ -10,6 +10,9 @@
 // are bitwise reproducible, as the reference's tests require (tests/test_grad_reduce.py:193).
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+#include <string>
+
 #include "common/layout.h"
 #include "device/sync.cuh"
 #include "device/tma.cuh"
@@ -21,8 +24,9 @@ namespace mep {
 constexpr int GR_MAX_TENSORS = 3;
 constexpr int GR_ACC_THREADS = 128;
 constexpr int GR_THREADS = 32 + GR_ACC_THREADS;
-constexpr uint32_t GR_CHUNK = 16 * 1024;              // bytes; 4096 floats
-constexpr int GR_VEC_PER_THREAD = GR_CHUNK / 16 / GR_ACC_THREADS;  // 8 float4 per thread
+// Chunk size (bytes) is a template parameter of the kernel: 32 KB chunks in a 6-stage ring on a
+// real group (64 KB chunks need 128 accumulator registers per thread and spill), 16 KB chunks in
+// the single-GPU virtual group, whose CTAs must share the SMs.
 
 struct GradReduceParams {
   SyncCtx sync;
@@ -34,8 +38,9 @@ struct GradReduceParams {
   int64_t rank_stride[GR_MAX_TENSORS];    // elements
 };
 
-template <int ST>
+template <int ST, uint32_t GR_CHUNK>
 __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const GradReduceParams p) {
+  constexpr int GR_VEC_PER_THREAD = GR_CHUNK / 16 / GR_ACC_THREADS;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full[ST];
   __shared__ __align__(8) uint64_t empty[ST];
@@ -181,31 +186,45 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
   // every home rank has read what it needs before anyone clears
   cross_rank_barrier(sc, 2);
   if (!p.zero_consumed) return;
-  // clear my consumed slots (local memory): 16-byte stores from every thread of the grid
-  for (int b = 0; b < epn; ++b) {
-    if (etc[rank * epn + b] < 0) continue;
-    for (int t = 0; t < p.n_tensors; ++t) {
-      float4* z = reinterpret_cast<float4*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
-                                            (size_t)b * p.expert_elems[t]);
-      const int64_t nv = p.expert_elems[t] / 4;
-      for (int64_t v = (int64_t)c * GR_THREADS + tid; v < nv; v += (int64_t)G * GR_THREADS)
-        z[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // clear my consumed slots (local memory): the first ring stage becomes a block of zeros that one
+  // thread per CTA bulk-stores over this CTA's share of every consumed slot (the copy engine
+  // writes full lines at a rate that per-thread 16-byte stores of 160 threads do not reach)
+  for (uint32_t i = (uint32_t)tid * 16u; i < GR_CHUNK; i += GR_THREADS * 16u)
+    *reinterpret_cast<uint4*>(ring + i) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0) {
+    int pending = 0;
+    for (int b = 0; b < epn; ++b) {
+      if (etc[rank * epn + b] < 0) continue;
+      for (int t = 0; t < p.n_tensors; ++t) {
+        uint8_t* z = reinterpret_cast<uint8_t*>(p.pool[t] + (size_t)rank * p.rank_stride[t] +
+                                                (size_t)b * p.expert_elems[t]);
+        const int64_t bytes = p.expert_elems[t] * 4;
+        for (int64_t off = (int64_t)c * GR_CHUNK; off < bytes; off += (int64_t)G * GR_CHUNK) {
+          const int64_t n = bytes - off < (int64_t)GR_CHUNK ? bytes - off : (int64_t)GR_CHUNK;
+          bulk_s2g(z + off, ring, (uint32_t)n);
+          if (++pending == 8) { bulk_commit(); pending = 0; }
+        }
+      }
     }
+    bulk_commit();
+    bulk_wait<0>();
   }
 }
 
-template <int ST>
+template <int ST, uint32_t GR_CHUNK>
 static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, cudaStream_t stream) {
   size_t smem = (size_t)ST * GR_CHUNK + sizeof(int32_t) * ((size_t)3 * c.epn + (size_t)c.epn * c.R);
   if (smem > 220 * 1024) return fail(-2, "reduce_grad: E=%d is too large for the slot lists", c.E);
   static thread_local size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_grad_reduce_kernel<ST>,
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_grad_reduce_kernel<ST, GR_CHUNK>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid(c.num_sms_weights, c.Rv());
-  MEP_CUDA_OK(launch_coop_paired((const void*)ep_grad_reduce_kernel<ST>, grid, dim3(GR_THREADS), smem, stream, p));
+  MEP_CUDA_OK(launch_coop_paired((const void*)ep_grad_reduce_kernel<ST, GR_CHUNK>, grid, dim3(GR_THREADS), smem, stream, p));
   return 0;
 }
 
@@ -240,9 +259,25 @@ int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* co
     p.local[t] = (float*)local[t]; p.pool[t] = (float*)pool[t];
     p.expert_elems[t] = expert_elems[t]; p.rank_stride[t] = rank_stride[t];
   }
-  if (c.virt) return launch_gr_t<4>(c, p, stream);
-  // a pull is bound by bytes in flight over the remote read latency: take what shared memory allows
-  return launch_gr_t<13>(c, p, stream);
+  if (c.virt) return launch_gr_t<4, 16 * 1024>(c, p, stream);
+  // ring geometry: MOONEP_B200_GR_RING = <stages>x<KB> selects one of the built variants (tuning)
+  static int cfg = -1;
+  if (cfg < 0) {
+    const char* e = getenv("MOONEP_B200_GR_RING");
+    cfg = 0;
+    if (e != nullptr) {
+      const std::string v(e);
+      cfg = v == "4x16" ? 1 : v == "8x16" ? 2 : v == "12x16" ? 3 : v == "16x8" ? 4 : v == "4x32" ? 5 : v == "6x32" ? 6 : 0;
+    }
+  }
+  switch (cfg) {
+    case 1: return launch_gr_t<4, 16 * 1024>(c, p, stream);
+    case 3: return launch_gr_t<12, 16 * 1024>(c, p, stream);
+    case 4: return launch_gr_t<16, 8 * 1024>(c, p, stream);
+    case 5: return launch_gr_t<4, 32 * 1024>(c, p, stream);
+    case 6: return launch_gr_t<6, 32 * 1024>(c, p, stream);
+    default: return launch_gr_t<8, 16 * 1024>(c, p, stream);
+  }
 }
 
 // Pure cross-rank barrier (one CTA per rank).

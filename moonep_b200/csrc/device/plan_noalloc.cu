@@ -107,18 +107,14 @@ extern "C" int mep_plan_local_noalloc(const int32_t* tpe_all, const int32_t* top
   const int64_t NvS = nvs_rows(S, K, E / R, token_padding);
   if (NvS > MAX_NVS || (int64_t)R * NvS > INT32_MAX)
     return fail(-3, "plan_local_noalloc: NvS=%lld does not fit the slot encoding", (long long)NvS);
-  // Device address of the static array, looked up once per device with that device current.
-  // The array's name is only a host-side handle here; a kernel must be given this address.
-  static int32_t* dev_ptr[64] = {nullptr};
-  int dev = 0;
-  MEP_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(-4, "plan_local_noalloc: device index %d not supported", dev);
-  if (dev_ptr[dev] == nullptr) {
-    void* ptr = nullptr;
-    MEP_CUDA_OK(cudaGetSymbolAddress(&ptr, g_plan_scratch));
-    dev_ptr[dev] = (int32_t*)ptr;
-  }
-  int32_t* scratch = dev_ptr[dev];
+  // Device address of the static array for the CURRENT device.  The array's name is only a
+  // host-side handle here; a kernel must be given this address.  It is looked up on every call (a
+  // host-side table lookup once the module is loaded) rather than cached: nothing can go stale
+  // after a device reset, and host threads share no mutable state.
+  void* ptr = nullptr;
+  MEP_CUDA_OK(cudaGetSymbolAddress(&ptr, g_plan_scratch));
+  if (ptr == nullptr) return fail(-4, "plan_local_noalloc: the scratch array has no device address");
+  int32_t* scratch = (int32_t*)ptr;
   LocalPlanParams lp;
   PlanParams& p = lp.plan;
   p.sync.rank_base = rank; p.sync.R = R; p.sync.meta = nullptr; p.sync.meta_stride = 0;

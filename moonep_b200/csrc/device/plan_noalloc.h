@@ -16,8 +16,10 @@
 //   * R * E <= MEP_NOALLOC_MAX_RE (16384, e.g. E = 2048 experts on 8 ranks); larger problems
 //     are rejected with an error, nothing is launched.
 //   * the array (about 257 KB) is resident on every GPU that loads the library until exit.
-//   * the FIRST call on a device looks the array's device address up (cudaGetSymbolAddress with
-//     that device current).  Make that first call outside any stream capture.
+//   * every call looks the array's device address up (cudaGetSymbolAddress with the calling
+//     thread's current device); the FIRST call on a device also loads the module.  Make that
+//     first call outside any stream capture.  Nothing is cached on the host, so a device reset
+//     between calls is harmless and host threads share no state here.
 //   * all calls on a device share the array, and it keeps what the last call left there; the
 //     kernel clears the words that must start at zero.  Two calls that overlap on the GPU (two
 //     streams, or two host threads) race on it: serialise them.

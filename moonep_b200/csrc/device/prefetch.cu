@@ -20,7 +20,8 @@ namespace mep {
 
 constexpr int PF_MAX_TENSORS = 6;
 constexpr int PF_THREADS = 64;
-constexpr uint32_t PF_CHUNK = 16 * 1024;
+// Chunk size (bytes) is a template parameter of the kernel: 32 KB on a real group, 16 KB in the
+// single-GPU virtual group, whose CTAs must share the SMs.
 
 struct PrefetchParams {
   SyncCtx sync;
@@ -32,7 +33,7 @@ struct PrefetchParams {
   int64_t rank_stride[PF_MAX_TENSORS];      // bytes between ranks' pools
 };
 
-template <int ST>
+template <int ST, uint32_t PF_CHUNK>
 __global__ void __launch_bounds__(PF_THREADS, 1) ep_prefetch_kernel(const PrefetchParams p) {
   constexpr int LA = ST / 2;
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -161,18 +162,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) ep_prefetch_kernel(const Prefet
   cross_rank_barrier(sc, 2);  // prefetched weights are visible on every rank
 }
 
-template <int ST>
+template <int ST, uint32_t PF_CHUNK>
 static int launch_prefetch_t(const BufferCtx& c, PrefetchParams& p, cudaStream_t stream) {
   size_t smem = (size_t)ST * PF_CHUNK + sizeof(int32_t) * ((size_t)4 * c.epn + (size_t)c.epn * c.R);
   if (smem > 220 * 1024) return fail(-2, "prefetch: E=%d is too large for the slot lists", c.E);
   static thread_local size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
-    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_prefetch_kernel<ST>,
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)ep_prefetch_kernel<ST, PF_CHUNK>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
   dim3 grid(c.num_sms_weights, c.Rv());
-  MEP_CUDA_OK(launch_coop_paired((const void*)ep_prefetch_kernel<ST>, grid, dim3(PF_THREADS), smem, stream, p));
+  MEP_CUDA_OK(launch_coop_paired((const void*)ep_prefetch_kernel<ST, PF_CHUNK>, grid, dim3(PF_THREADS), smem, stream, p));
   return 0;
 }
 
@@ -199,8 +200,8 @@ int mep_launch_prefetch(const void* ctx_, const int32_t* etc, int n, const void*
     p.local[t] = (const uint8_t*)local[t]; p.pool[t] = (uint8_t*)pool[t];
     p.expert_bytes[t] = expert_bytes[t]; p.rank_stride[t] = rank_stride[t];
   }
-  if (c.virt) return launch_prefetch_t<4>(c, p, stream);
-  return launch_prefetch_t<8>(c, p, stream);
+  if (c.virt) return launch_prefetch_t<4, 16 * 1024>(c, p, stream);
+  return launch_prefetch_t<6, 32 * 1024>(c, p, stream);
 }
 
 }  // extern "C"

@@ -71,6 +71,33 @@ def test_no_alloc_planner_matches_buffer_planner_twice():
     buf.destroy()
 
 
+@pytest.mark.parametrize("R,E,S,K,tp", [(2, 8192, 64, 4, 8), (64, 256, 48, 8, 16)])
+def test_no_alloc_planner_at_its_limits(R, E, S, K, tp):
+    """R * E = 16384 fills the whole built-in array and needs more than 48 KB of shared memory;
+    R = 64 takes the arg-max loops that stride over more ranks than a warp has lanes.  Checked
+    against the CPU oracle, twice in a row for two ranks."""
+    from moonep_b200 import _native
+    from moonep_b200 import reference as ref
+    fn = _symbol()
+    g = torch.Generator().manual_seed(R + E)
+    pop = torch.exp(1.5 * torch.randn(E, generator=g))
+    topk = torch.stack([torch.stack([torch.multinomial(pop, K, generator=g) for _ in range(S)])
+                        for _ in range(R)]).to(torch.int32)
+    tpe = torch.stack([torch.bincount(topk[r].flatten().long(), minlength=E) for r in range(R)]).to(torch.int32)
+    tables, dst = ref.plan_all_ranks(topk, S, K, E, tp, tpe)
+    tpe_d = tpe.cuda().contiguous()
+    for rank in (R - 1, 0):
+        rc, out = _call(fn, tpe_d, topk[rank].cuda().contiguous().view(-1), rank, R, E, S, K, tp)
+        torch.cuda.synchronize()
+        assert rc == 0, _native.last_error()
+        assert out["status"].tolist()[0] == 0
+        assert torch.equal(out["dst"].cpu(), dst[rank])
+        assert torch.equal(out["cu"].cpu(), tables.cu_seqlens[rank])
+        assert torch.equal(out["zf"].cpu(), tables.zero_fill[rank])
+        assert torch.equal(out["etc"].cpu(), tables.experts_to_copy)
+        assert torch.equal(out["rs"].cpu(), tables.remote_stats[rank])
+
+
 def test_no_alloc_planner_rejects_oversize():
     from moonep_b200 import _native
     fn = _symbol()
