@@ -369,6 +369,9 @@ def run_ours(args):
         if R > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        if buf.enable_phase_stamps():       # only with a library built with -DMEP_PHASE_STAMPS
+            eager_step(xs[0])
+            out["phase_stamps_us_rank0"] = buf.phase_stamps()
         out["trace_ms_max_over_ranks"] = {n: round(float(v), 3) for n, v in zip(names, t)}
         out["trace_ms_min_over_ranks"] = {n: round(float(v), 3) for n, v in zip(names, tmin)}
     if rank == 0:

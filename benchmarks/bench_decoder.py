@@ -2,7 +2,7 @@
 NCCL all-to-all baseline with no redundant experts (run under torch.distributed.run).
 
 Defaults: hidden 2048, 16 heads, seq 4096 (micro-batch 1 per rank), 8 layers, 128 SwiGLU experts
-with H'=768, top-8, vocab 32000, uniform random token ids, router bias searched for MaxVio >= 4.
+with H'=768, top-8, vocab 32000, uniform random token ids with targets that are a fixed function of the token, router bias searched for MaxVio >= 4.
 
   python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/bench_decoder.py
 """
@@ -50,8 +50,14 @@ def main():
     R, rank = dist.get_world_size(), dist.get_rank()
     S, Hd, E, K, Hp = args.seq, args.hidden, args.experts, args.topk, args.ffn
     gen = torch.Generator(device=dev).manual_seed(17 + rank)
-    batches = [(torch.randint(0, args.vocab, (S,), device=dev, generator=gen),
-                torch.randint(0, args.vocab, (S,), device=dev, generator=gen)) for _ in range(4)]
+    # Synthetic but LEARNABLE data: token ids are uniform random, the target of a position is a fixed
+    # function of its token (an affine map modulo the vocabulary), so the loss falls from ln(vocab)
+    # within the timed steps and a run shows that the stack trains, not only that it runs.
+    def batch():
+        tok = torch.randint(0, args.vocab, (S,), device=dev, generator=gen)
+        return tok, (tok * 31 + 7) % args.vocab
+
+    batches = [batch() for _ in range(4)]
     order = torch.randperm(E, generator=torch.Generator().manual_seed(99))
     ranks_ = torch.empty(E)
     ranks_[order] = torch.arange(1, E + 1, dtype=torch.float32)

@@ -44,6 +44,10 @@ nat.declare("mep_ctx_create", P, [I, I, I, I, I, I, I, I, I, I, I, P, L, P, L, P
 nat.declare("mep_ctx_destroy", None, [P])
 nat.declare("mep_ctx_set_second_shard", I, [P, P])
 nat.declare("mep_ctx_set_pdl", None, [P, I])
+nat.declare("mep_phase_stamps_compiled", I, [])
+nat.declare("mep_trace_ints64", L, [])
+nat.declare("mep_trace_dims", None, [ctypes.POINTER(ctypes.c_int)])
+nat.declare("mep_ctx_set_trace", None, [P, P])
 nat.declare("mep_launch_plan", I, [P, P, P, P, P, P, P, P, P, P])
 nat.declare("mep_launch_arrive_reset", I, [P, P])
 nat.declare("mep_launch_plan_snapshot", I, [P, P, P, P])
@@ -53,7 +57,7 @@ nat.declare("mep_launch_expand", I, [P, P, P, I, P])
 nat.declare("mep_launch_combine_prologue", I, [P, P, P, P])
 nat.declare("mep_launch_combine", I, [P, P, P, P, P])
 nat.declare("mep_launch_prefetch", I, [P, P, I, P, P, P, P, P])
-nat.declare("mep_launch_grad_reduce", I, [P, P, I, P, P, P, P, I, I, P])
+nat.declare("mep_launch_grad_reduce", I, [P, P, I, P, P, P, P, I, I, I, P])
 nat.declare("mep_launch_sync", I, [P, P])
 
 _KERNEL_NAMES = {1: "sync", 2: "plan", 3: "dispatch", 4: "expand", 5: "combine_prologue",
@@ -676,10 +680,12 @@ class Buffer:
             entry_sync=entry_sync, zero_consumed=zero_consumed)
 
     def reduce_grad_tensors(self, plan: CommPlan, locals_, pools, async_finish: bool = False, *,
-                            entry_sync: bool = True, zero_consumed: bool = True):
+                            entry_sync: bool = True, zero_consumed: bool = True, num_sms: int = 0):
         """``reduce_grad`` for any subset of projections: ``locals_[i]`` ``[epn, ...]`` fp32 and its
         ``[R, epn, ...]`` reduce buffer ``pools[i]``.  A training loop that finishes the down
-        projection's weight grads long before the gate/up ones can send them home early."""
+        projection's weight grads long before the gate/up ones can send them home early.
+        ``num_sms`` overrides the CTA count of this launch (default: ``num_sms_weights``): the last
+        reduce of a step runs next to nothing and may take more SMs."""
         self._require()
         assert plan is not None, "plan is required"
         locals_, pools = list(locals_), list(pools)
@@ -692,7 +698,7 @@ class Buffer:
 
         def run():
             self._rc(nat.call("mep_launch_grad_reduce", self._ctx, plan.experts_to_copy.data_ptr(), n,
-                              lp, pp, eb, rs, int(entry_sync), int(zero_consumed), self._stream()), "reduce_grad")
+                              lp, pp, eb, rs, int(entry_sync), int(zero_consumed), int(num_sms), self._stream()), "reduce_grad")
             self._stats["reduce_grad"] += 1
             self._maybe_check()
 
@@ -701,6 +707,51 @@ class Buffer:
             return ev
         run()
         return None
+
+    # ---- device-side phase stamps ---------------------------------------------------------------
+    _TRACE_NAMES = {
+        0: ("dispatch", ["set up", "past entry barrier", "rows issued", "past exit barrier"]),
+        1: ("combine", ["set up", "past entry barrier", "tokens stored"]),
+        2: ("fused_gemm.producer", ["start", "first group arrived", "last load issued"]),
+        3: ("fused_gemm.copy_warp", ["start", "all rows sent"]),
+    }
+
+    def enable_phase_stamps(self) -> bool:
+        """Start recording per-CTA ``%globaltimer`` stamps in the dispatch, combine and fused-GEMM
+        kernels.  Needs a library built with ``MOONEP_B200_NVCC_FLAGS=-DMEP_PHASE_STAMPS`` (a
+        normal build compiles the stamps out); returns ``False`` otherwise."""
+        self._require()
+        if not nat.call("mep_phase_stamps_compiled"):
+            return False
+        if getattr(self, "_trace", None) is None:
+            self._trace = torch.zeros(int(nat.call("mep_trace_ints64")), dtype=torch.int64, device=self.meta_buf.device)
+            nat.call("mep_ctx_set_trace", self._ctx, self._trace.data_ptr())
+        else:
+            self._trace.zero_()
+        return True
+
+    def phase_stamps(self) -> dict:
+        """``{kernel: {phase: (min_us, max_us)}}`` of the LAST launch of each stamped kernel, in
+        microseconds after the kernel's earliest stamp, over the CTAs that ran (synchronises)."""
+        if getattr(self, "_trace", None) is None:
+            return {}
+        torch.cuda.synchronize(self.device)
+        dims = (ctypes.c_int * 3)()
+        nat.call("mep_trace_dims", dims)
+        t = self._trace.view(dims[0], dims[1], dims[2]).cpu()
+        out = {}
+        for k, (name, phases) in self._TRACE_NAMES.items():
+            used = t[k][:, 0] > 0
+            if not bool(used.any()):
+                continue
+            t0 = int(t[k][used][:, 0].min())
+            out[name] = {}
+            for i, ph in enumerate(phases):
+                col = t[k][used][:, i]
+                col = col[col > 0]
+                if col.numel():
+                    out[name][ph] = (round((int(col.min()) - t0) / 1e3, 1), round((int(col.max()) - t0) / 1e3, 1))
+        return out
 
     # ---- telemetry ------------------------------------------------------------------------------
     def stats(self) -> dict:

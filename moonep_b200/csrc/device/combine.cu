@@ -244,7 +244,9 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
   }
   __syncthreads();
   pdl_wait();                 // this rank's pre-reduction kernel has completed
+  if (tid == 0) phase_stamp(sc.trace, 1, c, 0);
   cross_rank_barrier(sc, 1);  // every rank's shard (and its pre-reduction) is final
+  if (tid == 0) phase_stamp(sc.trace, 1, c, 1);          // past the entry barrier: pulls start
 
   const int32_t* dst = p.dst + (size_t)vr * p.N;
   const int n_tok = c < p.S ? (p.S - c + G - 1) / G : 0;
@@ -319,6 +321,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, 1) ep_combine_kernel(const Co
       w_out[e] = __int_as_float(bits);
     }
   }
+  if (tid == 32) phase_stamp(sc.trace, 1, c, 2);         // this CTA's tokens are summed and stored
 }
 
 // ---- pushed combine: barrier, then every rank sums the K rows its peers pushed per token -------

@@ -63,7 +63,9 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
   __syncthreads();
   pdl_launch_dependents();   // the expansion kernel may be scheduled; it waits for this one to end
   pdl_wait();                // a preceding planner launch has completed: its plan is readable
+  if (tid == 0) phase_stamp(sc.trace, 0, c, 0);          // set up, predecessor complete
   if (p.entry_barrier) cross_rank_barrier(sc, 1);
+  if (tid == 0) phase_stamp(sc.trace, 0, c, 1);          // past the entry barrier
 
   const __nv_bfloat16* x = p.x + (size_t)vr * p.S * p.H;
   const int32_t* dst = p.dst + (size_t)vr * p.N;
@@ -149,8 +151,10 @@ __global__ void __launch_bounds__(DISPATCH_THREADS, 1) ep_dispatch_kernel(const 
     }
     if (warp == 2 && lane == 0) { bulk_commit(); bulk_wait<0>(); fence_proxy_async(); }
   }
+  if (tid == 0) phase_stamp(sc.trace, 0, c, 2);          // this CTA's rows, weights and padding issued
   fence_sys();
   cross_rank_barrier(sc, 2);
+  if (tid == 0) phase_stamp(sc.trace, 0, c, 3);          // past the exit barrier
 
   if (p.link_out != nullptr) {
     const int32_t* src = sc.meta + (size_t)rank * sc.meta_stride + p.link_off;

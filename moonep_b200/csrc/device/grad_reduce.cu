@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(GR_THREADS, 1) ep_grad_reduce_kernel(const Gra
 }
 
 template <int ST, uint32_t GR_CHUNK>
-static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, cudaStream_t stream) {
+static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, int grid_x, cudaStream_t stream) {
   size_t smem = (size_t)ST * GR_CHUNK + sizeof(int32_t) * ((size_t)3 * c.epn + (size_t)c.epn * c.R);
   if (smem > 220 * 1024) return fail(-2, "reduce_grad: E=%d is too large for the slot lists", c.E);
   static thread_local size_t configured = 0;
@@ -223,7 +223,7 @@ static int launch_gr_t(const BufferCtx& c, GradReduceParams& p, cudaStream_t str
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     configured = smem;
   }
-  dim3 grid(c.num_sms_weights, c.Rv());
+  dim3 grid(grid_x > 0 ? grid_x : c.num_sms_weights, c.Rv());
   MEP_CUDA_OK(launch_coop_paired((const void*)ep_grad_reduce_kernel<ST, GR_CHUNK>, grid, dim3(GR_THREADS), smem, stream, p));
   return 0;
 }
@@ -241,11 +241,12 @@ using namespace mep;
 extern "C" {
 
 // etc [Rv][R*epn]; per tensor: local grad [Rv][epn][elems] fp32, pool base, elements per expert
-// (multiple of 4), element stride between ranks' pools.
+// (multiple of 4), element stride between ranks' pools.  grid_x > 0 overrides the number of CTAs
+// (the Buffer's num_sms_weights): a reduce that runs next to nothing may take more SMs.
 int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* const* local,
                            void* const* pool, const int64_t* expert_elems,
                            const int64_t* rank_stride, int entry_barrier, int zero_consumed,
-                           cudaStream_t stream) {
+                           int grid_x, cudaStream_t stream) {
   const BufferCtx& c = *(const BufferCtx*)ctx_;
   if (n < 1 || n > GR_MAX_TENSORS) return fail(-1, "reduce_grad: %d tensors (1..%d)", n, GR_MAX_TENSORS);
   GradReduceParams p;
@@ -259,7 +260,7 @@ int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* co
     p.local[t] = (float*)local[t]; p.pool[t] = (float*)pool[t];
     p.expert_elems[t] = expert_elems[t]; p.rank_stride[t] = rank_stride[t];
   }
-  if (c.virt) return launch_gr_t<4, 16 * 1024>(c, p, stream);
+  if (c.virt) return launch_gr_t<4, 16 * 1024>(c, p, grid_x, stream);
   // ring geometry: MOONEP_B200_GR_RING = <stages>x<KB> selects one of the built variants (tuning)
   static int cfg = -1;
   if (cfg < 0) {
@@ -271,12 +272,12 @@ int mep_launch_grad_reduce(const void* ctx_, const int32_t* etc, int n, void* co
     }
   }
   switch (cfg) {
-    case 1: return launch_gr_t<4, 16 * 1024>(c, p, stream);
-    case 3: return launch_gr_t<12, 16 * 1024>(c, p, stream);
-    case 4: return launch_gr_t<16, 8 * 1024>(c, p, stream);
-    case 5: return launch_gr_t<4, 32 * 1024>(c, p, stream);
-    case 6: return launch_gr_t<6, 32 * 1024>(c, p, stream);
-    default: return launch_gr_t<8, 16 * 1024>(c, p, stream);
+    case 1: return launch_gr_t<4, 16 * 1024>(c, p, grid_x, stream);
+    case 3: return launch_gr_t<12, 16 * 1024>(c, p, grid_x, stream);
+    case 4: return launch_gr_t<16, 8 * 1024>(c, p, grid_x, stream);
+    case 5: return launch_gr_t<4, 32 * 1024>(c, p, grid_x, stream);
+    case 6: return launch_gr_t<6, 32 * 1024>(c, p, grid_x, stream);
+    default: return launch_gr_t<8, 16 * 1024>(c, p, grid_x, stream);
   }
 }
 

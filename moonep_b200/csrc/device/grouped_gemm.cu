@@ -105,6 +105,7 @@ struct GemmKParams {
   long long push_rank_stride;
   int push_entries, push_ranks;
   FusedDispatch disp;      // DISP kernels only
+  long long* trace;        // phase stamps of the fused launches (see sync.cuh), or null
   // DISP: budget of a wait for rows from other ranks.  It is shorter than timeout_ns, which bounds
   // the waits that only follow from it (the MMA thread on the operand ring, the epilogue on the
   // accumulator), so that a missing row is reported as what it is.
@@ -337,6 +338,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
       int it = 0;
       bool ok = true;
       int groups_ready = 0;      // DISP: groups [0, groups_ready) are known to have arrived
+      if constexpr (DISP) phase_stamp(p.trace, 2, (int)blockIdx.x, 0);       // producer starts
+      bool stamped_first = false;
       for (long long id = work_id0; id < total_tiles && ok; id += work_stride) {
         Tile t = get_tile<WGRAD, EPI, TWO>(p, (int)id, s_end, s_prefix, n_tiles_n, crank);
         if (!t.valid) continue;
@@ -362,6 +365,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             if (!ok) break;
             __threadfence_block();
             fence_proxy_async();   // the rows were written through the async proxy (or by plain stores)
+            if (!stamped_first) { phase_stamp(p.trace, 2, (int)blockIdx.x, 1); stamped_first = true; }   // first group arrived
 #ifdef MEP_GEMM_EXPERIMENTS
             if (p.status != nullptr)                   // experiments: total arrival wait of all CTAs, in microseconds
               atomicAdd(p.status + 6, (int)((globaltimer_ns() - t_begin) / 1000ull));
@@ -437,6 +441,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           }
         }
       }
+      if constexpr (DISP) phase_stamp(p.trace, 2, (int)blockIdx.x, 2);       // last operand load issued
     } else if (DISP && p.disp.arrive != nullptr) {
       // ---- arrival watchers (lanes 1..31): group after group, wait until every 128-row block of
       // the group has all its rows, then publish the number of complete groups to lane 0 --------
@@ -504,9 +509,11 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
 #ifdef MEP_GEMM_EXPERIMENTS
         const unsigned long long t_begin = globaltimer_ns();
 #endif
+        if (lane == 0) phase_stamp(p.trace, 3, (int)blockIdx.x, 0);          // copy warp starts
         fused_dispatch_copy_warp<FD_NST>(
             p.disp, ring, fd_full, (int)blockIdx.x, (int)gridDim.x,
             [&](uint64_t* bar, uint32_t parity) { return gemm_wait(bar, parity, abortp, p, 7); });
+        if (lane == 0) phase_stamp(p.trace, 3, (int)blockIdx.x, 1);          // all rows sent and announced
 #ifdef MEP_GEMM_EXPERIMENTS
         if (lane == 0 && p.status != nullptr)      // experiments: longest copy-warp run, in microseconds
           atomicMax(p.status + 7, (int)((globaltimer_ns() - t_begin) / 1000ull));
@@ -1203,6 +1210,7 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       f.x = (const uint8_t*)d->disp_x; f.w = d->disp_w; f.dst = d->disp_dst; f.order = d->disp_order;
       f.zero_fill = d->disp_zero_fill;
     }
+    kp.trace = c.trace;
     kp.arrive_timeout_ns = c.timeout_ns;                       // waits on other ranks: the Buffer's budget
     kp.timeout_ns = c.timeout_ns + c.timeout_ns / 2 + 200000000ull;
 #ifdef MEP_GEMM_EXPERIMENTS

@@ -117,7 +117,7 @@ extern "C" int mep_plan_local_noalloc(const int32_t* tpe_all, const int32_t* top
   int32_t* scratch = (int32_t*)ptr;
   LocalPlanParams lp;
   PlanParams& p = lp.plan;
-  p.sync.rank_base = rank; p.sync.R = R; p.sync.meta = nullptr; p.sync.meta_stride = 0;
+  p.sync.trace = nullptr; p.sync.rank_base = rank; p.sync.R = R; p.sync.meta = nullptr; p.sync.meta_stride = 0;
   p.sync.flags_off = 0;
   p.sync.sync_state = scratch + NOALLOC_TABLE_INTS;       // [8], abort flag at word 2
   p.sync.status = scratch + NOALLOC_TABLE_INTS + 8;       // [8]

@@ -38,7 +38,27 @@ enum KernelId : int {
 //   [0] grid barrier word   [1] barrier epoch   [2] abort flag   [3] plan parity
 constexpr int SYNC_STATE_INTS = 8;
 
+// Device-side phase stamps (tracing): with -DMEP_PHASE_STAMPS a kernel's CTAs record
+// %globaltimer at a few named points into trace[kernel][cta][phase] (int64 ns), which the host
+// reads after the run (Buffer.phase_stamps(), bench.py --trace).  Without the flag phase_stamp()
+// is empty and the kernels carry nothing of it.
+constexpr int TRACE_KERNELS = 4;      // 0 dispatch, 1 combine, 2 fused GEMM producer, 3 fused GEMM copy warp
+constexpr int TRACE_CTAS = 320;
+constexpr int TRACE_PHASES = 8;
+#ifdef MEP_PHASE_STAMPS
+__device__ __forceinline__ void phase_stamp(long long* trace, int kernel, int cta, int phase) {
+  if (trace != nullptr && cta < TRACE_CTAS && phase < TRACE_PHASES) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    trace[((size_t)kernel * TRACE_CTAS + cta) * TRACE_PHASES + phase] = (long long)t;
+  }
+}
+#else
+__device__ __forceinline__ void phase_stamp(long long*, int, int, int) {}
+#endif
+
 struct SyncCtx {
+  long long* trace;        // phase stamps, or null (see phase_stamp)
   int rank_base;
   int R;
   int32_t* meta;           // symmetric meta buffer, chunk of rank 0

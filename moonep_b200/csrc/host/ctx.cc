@@ -47,6 +47,7 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
   c->plan_scratch_ints = plan_scratch_ints(R, E, num_sms);
   c->timeout_ns = (unsigned long long)timeout_ns;
   c->pdl = 0;
+  c->trace = nullptr;
   int dev = 0;
   c->sm_count = 0;
   if (cudaGetDevice(&dev) == cudaSuccess)
@@ -55,6 +56,21 @@ void* mep_ctx_create(int rank, int R, int virt, int E, int S, int K, int H, int 
 }
 
 void mep_ctx_destroy(void* ctx) { delete (BufferCtx*)ctx; }
+
+// Phase stamps: 1 when the library was built with -DMEP_PHASE_STAMPS; the buffer holds
+// mep_trace_ints64() int64 words (kernels x CTAs x phases).
+int mep_phase_stamps_compiled() {
+#ifdef MEP_PHASE_STAMPS
+  return 1;
+#else
+  return 0;
+#endif
+}
+int64_t mep_trace_ints64() { return (int64_t)TRACE_KERNELS * TRACE_CTAS * TRACE_PHASES; }
+void mep_trace_dims(int* out) { out[0] = TRACE_KERNELS; out[1] = TRACE_CTAS; out[2] = TRACE_PHASES; }
+void mep_ctx_set_trace(void* ctx, void* trace) {
+  if (ctx != nullptr) ((BufferCtx*)ctx)->trace = (long long*)trace;
+}
 
 // Programmatic dependent launch of the kernel chains (Buffer(enable_pdl=...)).
 void mep_ctx_set_pdl(void* ctx, int enable) {

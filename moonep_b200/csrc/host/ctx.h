@@ -31,6 +31,7 @@ struct BufferCtx {
   int64_t plan_scratch_ints;
   unsigned long long timeout_ns;
   int sm_count;
+  long long* trace;        // device buffer of phase stamps, or null
   int pdl;                 // chain plan -> dispatch -> expand and prologue -> combine programmatically
 
   int Rv() const { return virt ? R : 1; }
@@ -43,6 +44,7 @@ struct BufferCtx {
   // flight at the same time (on different streams) without disturbing the other's barriers.
   SyncCtx sync(int kernel_id, int channel = 0) const {
     SyncCtx s;
+    s.trace = trace;
     s.rank_base = virt ? 0 : rank;
     s.R = R;
     s.meta = meta;

@@ -262,9 +262,11 @@ class _MoEFn(torch.autograd.Function):
                        grid=layer.overlap_grid() if do_reduce else 0)
         if layer.hidden_in_place:      # the forward rows have had their last reader
             layer.buf.release_second_shard(layer)
-        if do_reduce:         # and the up grads under the combine and the router backward
+        if do_reduce:         # and the up grads under the combine and the router backward, which
+            # leave most SMs idle: this last reduce is what the step waits for, give it more CTAs
             ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
-                                                 async_finish=True, zero_consumed=zc)
+                                                 async_finish=True, zero_consumed=zc,
+                                                 num_sms=layer.last_reduce_sms)
         return ev_r
 
 
@@ -290,6 +292,8 @@ class MoELayer:
         # set to a learning rate to run the SGD step of the expert weights inside the weight-grad
         # epilogues of the next backward pass (see ``fuse_sgd``)
         self.fused_sgd_lr: Optional[float] = None
+        # CTAs of the step's last reduce_grad launch (0: the Buffer's num_sms_weights)
+        self.last_reduce_sms = max(buf.num_sms_weights, 48) // 2 * 2
         self._sgd_keep = None
         self.tracer = NULL_TRACER
         if fused_combine:

@@ -221,3 +221,28 @@ def test_programmatic_dependent_launch_gives_identical_results(R):
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
     for u, v in zip(a[4], b[4]):
         assert torch.equal(u, v)
+
+
+def test_phase_stamps_when_compiled_in():
+    """With a library built with -DMEP_PHASE_STAMPS the dispatch and combine kernels record
+    per-CTA %globaltimer stamps; the phases of a kernel are ordered in time.  A normal build has
+    no stamps (the call says so) and the test is skipped."""
+    from moonep_b200 import Buffer
+    from moonep_b200.utils.routing import routing_for_maxvio, tokens_per_expert
+    R, S, H, K, tp = 2, 128, 256, 4, 16
+    E = 8 * R
+    buf = Buffer(S, H, K, E, R, num_sms=4, token_padding=tp, virtual=True, timeout_s=5.0)
+    if not buf.enable_phase_stamps():
+        buf.destroy()
+        pytest.skip("library built without -DMEP_PHASE_STAMPS")
+    topk, w, _, _ = routing_for_maxvio(S, K, E, R, 1.0, seed=2)
+    tpe = torch.stack([tokens_per_expert(topk[r], E) for r in range(R)]).cuda()
+    x = torch.randn(R, S, H, generator=torch.Generator().manual_seed(1)).bfloat16().cuda()
+    h, wn, cu, plan = buf.dispatch(x, w.cuda(), topk.cuda(), tpe)
+    buf.combine(plan, h, None)
+    st = buf.phase_stamps()
+    assert set(st) >= {"dispatch", "combine"}
+    d = st["dispatch"]
+    assert d["set up"][0] == 0.0 and d["past exit barrier"][1] >= d["rows issued"][0] >= 0.0
+    assert st["combine"]["tokens stored"][1] >= st["combine"]["past entry barrier"][0]
+    buf.destroy()
