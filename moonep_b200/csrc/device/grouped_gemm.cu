@@ -46,6 +46,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 
@@ -62,6 +63,10 @@ constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int GEMM_THREADS = 192;
+// SGD kernels: eight epilogue warps, two per quarter of the accumulator's lanes, each with one
+// half of the tile's columns (the read-modify-write stream of a warp is a chain of latencies:
+// accumulator load, weight block landed, update, store read; twice the warps run twice the chains)
+constexpr int GEMM_THREADS_SGD = 320;
 constexpr int GEMM_THREADS_DISP = 224;      // + the copy warp of the fused dispatch
 constexpr int MAX_GROUPS = 1024;
 // CTA-pair variant: each CTA stages A (16 KB) and half of B (16 KB) per k-block, six stages.
@@ -84,6 +89,7 @@ struct GemmKParams {
   // gemm_dbg() is a constant false and none of those branches exists.  Bit 16 (plain-store
   // epilogues, results stay correct) is a host-side choice of the epilogue and always available.
   int debug;
+  int stages, wb;   // SGD kernels: operand stages and weight blocks per epilogue warp of this launch
   int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
   int tma_out; // outputs are 16-byte aligned: whole 32-row blocks leave through TMA stores
   // weight grad fused with the SGD step: a local expert's tile is applied straight to its bf16
@@ -232,7 +238,10 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
 template <bool TWO, bool SGD, bool DISP = false> __host__ __device__ constexpr int gemm_stages() {
   return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (SGD ? 1 : 0) - (DISP ? 1 : 0);
 }
-template <bool TWO> __host__ __device__ constexpr int sgd_ring() { return TWO ? 2 : 3; }   // 4 KB weight blocks per warp
+// The SGD kernels take their ring geometry at launch (GemmKParams::stages / wb): how the shared
+// memory is best split between operand stages and weight blocks depends on the group length.
+constexpr int SGD_RING_MAX = 8;      // 4 KB weight blocks per epilogue warp, at most
+template <bool TWO> __host__ __device__ constexpr int sgd_ring() { return TWO ? 2 : 3; }   // geometry of gemm_smem<.., SGD>()
 // Fused dispatch: stages of the copy ring (the pair kernel with the staged bf16 epilogue has less
 // shared memory to spare).
 template <bool TWO, int EPI> __host__ __device__ constexpr int fd_stages() { return (TWO && EPI == EPI_BF16) ? 5 : 8; }
@@ -242,14 +251,17 @@ template <bool TWO, bool SGD, bool DISP = false, int EPI = EPI_BF16> __host__ __
 }
 
 template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false, bool SGD = false, bool DISP = false>
-__global__ void __launch_bounds__(DISP ? GEMM_THREADS_DISP : GEMM_THREADS, 1)
+__global__ void __launch_bounds__(SGD ? GEMM_THREADS_SGD : (DISP ? GEMM_THREADS_DISP : GEMM_THREADS), 1)
 ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   static_assert(!SGD || (WGRAD && EPI == EPI_F32), "the fused SGD step belongs to the weight grad");
   static_assert(!DISP || (!WGRAD && !SGD), "the fused dispatch feeds a token-major GEMM");
-  constexpr int GEMM_STAGES = gemm_stages<TWO, SGD, DISP>();
+  // operand stages: a constant, except in the SGD kernels (upper bound; p.stages are used)
+  constexpr int GEMM_STAGES = SGD ? (TWO ? GEMM_STAGES2 : mep::GEMM_STAGES) : gemm_stages<TWO, false, DISP>();
+  const int nst = SGD ? p.stages : GEMM_STAGES;
   constexpr int FD_NST = fd_stages<TWO, EPI>();
   constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
-  constexpr int WB = SGD ? sgd_ring<TWO>() : 1;
+  constexpr int WB_MAX = SGD ? SGD_RING_MAX : 1;
+  const int WB = SGD ? p.wb : 1;
   const int crank = TWO ? (int)cluster_cta_rank() : 0;        // 0 = leader of the pair
   const int work_id0 = TWO ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int work_stride = TWO ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -268,7 +280,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   __shared__ __align__(1024) float s_epi[(EPI == EPI_F32) ? 4 * 32 * 33 : 1];
   // fused SGD: per epilogue warp a ring of WB 32 x 32 bf16 weight blocks (in dynamic shared
   // memory, behind the operand stages) and their "landed" barriers
-  __shared__ __align__(8) uint64_t wbar[4][WB];
+  __shared__ __align__(8) uint64_t wbar[SGD ? 8 : 4][WB_MAX];
   __shared__ __align__(128) uint8_t s_push[(EPI == EPI_PUSH) ? 4 * 4096 : 16];
   // staging of the bf16 epilogue: per warp one 32 x 64 block (128-byte rows, 128B swizzle)
   __shared__ __align__(1024) uint8_t s_out[(!WGRAD && EPI == EPI_BF16) ? 4 * 4096 : 16];
@@ -283,8 +295,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     // CTA pairs: both CTAs' loads are credited to the LEADER's full barrier, which only the
     // leader's producer arrives on (expecting the bytes of both CTAs); no per-stage remote arrive
     for (int s = 0; s < GEMM_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], TWO ? 8 : 4); }
-    for (int a = 0; a < 4 * WB; ++a) mbar_init(&wbar[a / WB][a % WB], 1);
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], (TWO ? 8 : 4) * (SGD ? 2 : 1)); }
+    for (int a = 0; a < (SGD ? 8 : 4) * WB_MAX; ++a) mbar_init(&wbar[a / WB_MAX][a % WB_MAX], 1);
     if constexpr (DISP) for (int a = 0; a < FD_NST; ++a) mbar_init(&fd_full[a], 1);
     mbar_fence_init();
     s_abort = 0;
@@ -373,9 +385,9 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           }
         }
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-          const int s = it % GEMM_STAGES;
-          if (it >= GEMM_STAGES &&
-              !gemm_wait(&empty[s], ((uint32_t)(it / GEMM_STAGES) & 1u) ^ 1u, abortp, p, 1)) {
+          const int s = it % nst;
+          if (it >= nst &&
+              !gemm_wait(&empty[s], ((uint32_t)(it / nst) & 1u) ^ 1u, abortp, p, 1)) {
             ok = false;
             break;
           }
@@ -476,8 +488,8 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
         tc_fence_after();
         const uint32_t tacc = tmem_base + (uint32_t)acc * BN;
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
-          const int s = it % GEMM_STAGES;
-          if (!gemm_wait(&full[s], (uint32_t)(it / GEMM_STAGES) & 1u, abortp, p, 3)) { ok = false; break; }
+          const int s = it % nst;
+          if (!gemm_wait(&full[s], (uint32_t)(it / nst) & 1u, abortp, p, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t sb = sa + A_TILE_BYTES;
@@ -505,7 +517,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     // ================= fused dispatch: this CTA's share of the all-to-all =================
     if constexpr (DISP) {
       if (p.disp.x != nullptr) {
-        uint8_t* ring = tiles + (size_t)GEMM_STAGES * STAGE_BYTES;
+        uint8_t* ring = tiles + (size_t)nst * STAGE_BYTES;
 #ifdef MEP_GEMM_EXPERIMENTS
         const unsigned long long t_begin = globaltimer_ns();
 #endif
@@ -524,6 +536,11 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     // ================= epilogue (4 warps, one TMEM lane quarter each) =================
     const int q = warp & 3;
     const int r_in_tile = q * 32 + lane;
+    // SGD: warps 2..5 take the tile's first 128 columns, warps 6..9 the other 128
+    const int half = SGD ? (warp - 2) >> 2 : 0;
+    const int ew = q + 4 * half;
+    constexpr int CB = SGD ? BN / 64 / 2 : BN / 64;     // 64-column weight blocks per warp and tile
+    const int cofs = half * CB * 64;
     int tile_n = 0;
     // ---- fused SGD: weight blocks stream through this warp's ring, ahead of the tiles ----------
     // Block k of the stream (the 32-row x 64-column blocks of this warp's rows, tile after tile,
@@ -532,7 +549,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     // allows: the TMA engine moves about one box row per 5 cycles per SM whatever its length
     // (measured), so 64-byte rows cap this epilogue at half the HBM rate.
     constexpr int WBLK = 4096, WCOLS = 64;
-    uint8_t* wring = tiles + (size_t)GEMM_STAGES * STAGE_BYTES + q * (WB * WBLK);
+    uint8_t* wring = tiles + (size_t)nst * STAGE_BYTES + ew * (WB * WBLK);
     int wseq = 0, lseq = 0;                // blocks consumed / loads issued (a few thousand per launch)
     long long lid = work_id0;              // cursor: tile id, block in tile, cached coordinates
     int lc = 0, l_y0 = 0, l_n0 = 0;
@@ -546,7 +563,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           const Tile u = get_tile<WGRAD, EPI, TWO>(p, (int)lid, s_end, s_prefix, n_tiles_n, crank);
           if (sgd_tile(u)) { l_have = true; l_y0 = u.g_local * p.Mw + u.m0 + q * 32; l_n0 = u.n0; lc = 0; }
         }
-        if (l_have && lc < BN / WCOLS && l_n0 + lc * WCOLS < p.N) return;
+        if (l_have && lc < CB && l_n0 + cofs + lc * WCOLS < p.N) return;
         l_have = false;
         lid += work_stride;
       }
@@ -554,9 +571,9 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     auto issue_loads = [&]() {             // lane 0 issues; every lane tracks the cursor
       while (lid < total_tiles && lseq < wseq + WB) {
         if (lane == 0) {
-          uint64_t* bar = &wbar[q][lseq % WB];
+          uint64_t* bar = &wbar[ew][lseq % WB];
           mbar_expect_tx(bar, WBLK);
-          tma_load_2d(wring + (lseq % WB) * WBLK, &p.wmap, l_n0 + lc * WCOLS, l_y0, bar);
+          tma_load_2d(wring + (lseq % WB) * WBLK, &p.wmap, l_n0 + cofs + lc * WCOLS, l_y0, bar);
         }
         ++lseq;
         ++lc;
@@ -715,16 +732,16 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
             const float nlr = -p.sgd_lr;
             bool wok = true;
 #pragma unroll 1
-            for (int c = 0; c < BN / WCOLS; ++c) {
-              if (col_base + c * WCOLS >= p.N) break;
+            for (int c = 0; c < CB; ++c) {
+              if (col_base + cofs + c * WCOLS >= p.N) break;
               const int b = wseq % WB;
               uint8_t* wbuf = wring + b * WBLK;
               uint32_t ra[32], rb[32];
               if (!gemm_dbg(p, 2)) {
-                tmem_ld_32x32(tacc + c * WCOLS, ra);
-                tmem_ld_32x32(tacc + c * WCOLS + 32, rb);
+                tmem_ld_32x32(tacc + cofs + c * WCOLS, ra);
+                tmem_ld_32x32(tacc + cofs + c * WCOLS + 32, rb);
               }
-              if (!gemm_wait(&wbar[q][b], (uint32_t)(wseq / WB) & 1u, abortp, p, 5)) {
+              if (!gemm_wait(&wbar[ew][b], (uint32_t)(wseq / WB) & 1u, abortp, p, 5)) {
                 if (!gemm_dbg(p, 2)) tmem_ld_wait();
                 wok = false;
                 break;
@@ -753,7 +770,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               __syncwarp();
               if (lane == 0) {
                 if (!gemm_dbg(p, 1)) {
-                  tma_store_2d(&p.wmap, col_base + c * WCOLS, y0, wbuf);
+                  tma_store_2d(&p.wmap, col_base + cofs + c * WCOLS, y0, wbuf);
                   bulk_commit();
                 }
                 bulk_wait_read<0>();                // the store has read the buffer: it may be refilled
@@ -762,7 +779,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
               issue_loads();
             }
             if (!wok) break;
-          } else
+          } else if (half == 0)      // (SGD kernels: a tile that is not applied is stored by warps 2..5 alone)
 #pragma unroll 1
           for (int c = 0; c < BN / 32; ++c) {
             uint32_t r[32];
@@ -1013,20 +1030,54 @@ static bool fused_dispatch_cooperative() {
   return v != 0;
 }
 
+// SGD kernels: dynamic shared memory of a launch (operand stages, alignment slack, four rings of
+// 4 KB weight blocks) and the most that the kernel may ask for next to its static part.
+static int sgd_smem(const GemmKParams& kp, bool two) {
+  return kp.stages * (two ? STAGE_BYTES2 : STAGE_BYTES) + 1024 + 8 * kp.wb * 4096;
+}
+// How an SGD launch splits its shared memory between operand stages and weight blocks (4 KB, per
+// epilogue warp).  Measured on the benchmark's shapes (32 x 1024, 64 x 512, 256 x 128 rows): the
+// depth of the weight ring hardly matters once eight warps run the read-modify-write chains (a
+// warp needs ~1.4 us per block whatever the depth), so the operand ring gets what is left after
+// two (pairs) or three (single CTA, whose stages are 48 KB) blocks per warp.
+// MOONEP_B200_SGD_RING="stages,blocks" overrides the choice (tuning).
+static void sgd_geometry(bool pair, GemmKParams* kp) {
+  if (pair) { kp->stages = 4; kp->wb = 2; }
+  else { kp->stages = 2; kp->wb = 3; }
+  if (const char* e = getenv("MOONEP_B200_SGD_RING")) {
+    int a = 0, b = 0;
+    if (sscanf(e, "%d,%d", &a, &b) == 2 && a >= 2 && a <= (pair ? GEMM_STAGES2 : GEMM_STAGES) && b >= 2 &&
+        b <= SGD_RING_MAX) {
+      kp->stages = a; kp->wb = b;
+    }
+  }
+}
+static int sgd_smem_limit(const void* kern) {
+  cudaFuncAttributes fa;
+  int dev = 0, optin = 0;
+  if (cudaFuncGetAttributes(&fa, kern) != cudaSuccess) { cudaGetLastError(); return 0; }
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  return optin - (int)fa.sharedSizeBytes;
+}
+
 // CTA-pair launch: clusters of two CTAs, one pair per two SMs.
 template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false, bool DISP = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true, SGD, DISP>;
-  constexpr int GEMM_SMEM2 = gemm_smem<true, SGD, DISP, EPI>();
+  const int GEMM_SMEM2 = SGD ? sgd_smem(kp, true) : gemm_smem<true, SGD, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
-    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM2));
+    const int most = SGD ? sgd_smem_limit((const void*)kern) : GEMM_SMEM2;
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     configured = true;
   }
+  if (SGD && GEMM_SMEM2 > sgd_smem_limit((const void*)kern))
+    return fail(-3, "gemm: %d operand stages + %d weight blocks do not fit in shared memory", kp.stages, kp.wb);
   cudaLaunchConfig_t cfg;
   std::memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3((unsigned)(grid / 2 * 2));
-  cfg.blockDim = dim3(DISP ? GEMM_THREADS_DISP : GEMM_THREADS);
+  cfg.blockDim = dim3(SGD ? GEMM_THREADS_SGD : (DISP ? GEMM_THREADS_DISP : GEMM_THREADS));
   cfg.dynamicSmemBytes = GEMM_SMEM2;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -1068,12 +1119,15 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
 template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool SGD = false, bool DISP = false>
 static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
   auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, false, SGD, DISP>;
-  constexpr int GEMM_SMEM = gemm_smem<false, SGD, DISP, EPI>();
+  const int GEMM_SMEM = SGD ? sgd_smem(kp, false) : gemm_smem<false, SGD, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
-    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM));
+    const int most = SGD ? sgd_smem_limit((const void*)kern) : GEMM_SMEM;
+    MEP_CUDA_OK(cudaFuncSetAttribute((const void*)kern, cudaFuncAttributeMaxDynamicSharedMemorySize, most));
     configured = true;
   }
+  if (SGD && GEMM_SMEM > sgd_smem_limit((const void*)kern))
+    return fail(-3, "gemm: %d operand stages + %d weight blocks do not fit in shared memory", kp.stages, kp.wb);
   if constexpr (DISP) {
     // CTAs of different ranks wait for one another's copy warps: all of them must be resident
     int dev = 0, sms = 0;
@@ -1089,7 +1143,7 @@ static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
     }
     return 0;
   }
-  kern<<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(kp);
+  kern<<<grid, SGD ? GEMM_THREADS_SGD : GEMM_THREADS, GEMM_SMEM, stream>>>(kp);
   MEP_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -1111,6 +1165,9 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
   kp.rows_per_expert = d->rows_per_expert; kp.Mw = d->Mw; kp.accumulate = d->accumulate;
   kp.zero_empty_below = d->zero_empty_below;
   kp.debug = d->debug; kp.g_begin = d->g_begin;
+#ifdef MEP_GEMM_EXPERIMENTS
+  if (const char* e = getenv("MOONEP_B200_GEMM_EXPERIMENT")) kp.debug |= atoi(e);   // timing only: results are wrong
+#endif
   kp.src_info = d->src_info; kp.push_base = d->push_base; kp.push_rank_stride = d->push_rank_stride;
   kp.push_entries = d->push_entries; kp.push_ranks = d->push_ranks;
   kp.out[0] = d->out[0]; kp.out[1] = d->out[1]; kp.out[2] = d->out[2];
@@ -1144,6 +1201,7 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
       if ((rc = make_map_f32(&kp.c[1], d->out[1], (int64_t)(d->ngroups - d->split) * d->Mw, d->N, d->ldc))) return rc;
     }
     const bool pair = d->two_cta != 0 && grid >= 2 && d->Mw % (2 * BM) == 0;
+    if (kp.sgd_w != nullptr) sgd_geometry(pair, &kp);
     if (kp.sgd_w != nullptr)
       return pair ? launch_gemm2<true, true, EPI_F32, true, true>(kp, grid, stream)
                   : launch_gemm<true, true, true, EPI_F32, true>(kp, grid, stream);

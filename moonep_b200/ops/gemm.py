@@ -95,6 +95,7 @@ TWO_CTA = {"auto": 2, "": 2}.get(_two, None)
 if TWO_CTA is None:
     TWO_CTA = int(_two)
 PAIR_MIN_AVG_ROWS = 768
+PAIR_MIN_AVG_ROWS_WGRAD = 512   # 64 groups x 512 rows, fused SGD: pairs 1.16 ms, single CTAs 1.44 ms
 
 
 def _launch(d: _GemmDesc) -> None:
@@ -106,7 +107,8 @@ def _launch(d: _GemmDesc) -> None:
         # rows taken from those).  Weight-grad tiles split the weight rows instead, but with short
         # groups (a few k-blocks per tile) the pair's extra hand-shakes cost more than they save.
         local_groups = max(1, min(d.ngroups, d.split))
-        d.two_cta = int(d.grid % 2 == 0 and d.total_rows >= PAIR_MIN_AVG_ROWS * local_groups)
+        least = PAIR_MIN_AVG_ROWS_WGRAD if d.mode == 1 else PAIR_MIN_AVG_ROWS
+        d.two_cta = int(d.grid % 2 == 0 and d.total_rows >= least * local_groups)
     else:
         d.two_cta = TWO_CTA
     if not _checked_layout:
