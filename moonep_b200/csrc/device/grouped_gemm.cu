@@ -90,6 +90,10 @@ struct GemmKParams {
   // epilogues, results stay correct) is a host-side choice of the epilogue and always available.
   int debug;
   int stages, wb;   // SGD kernels: operand stages and weight blocks per epilogue warp of this launch
+  // SGD kernels: 1 = only the tiles whose grads are STORED (experts with replicas, slot groups),
+  // 2 = only the tiles that are applied to the weights, 0 = all.  Lets the grads that have to
+  // travel be computed first, so that their reduce runs beside the rest of the weight grad.
+  int wg_select;
   int g_begin; // groups below this index are skipped (a launch may cover a suffix of the groups)
   int tma_out; // outputs are 16-byte aligned: whole 32-row blocks leave through TMA stores
   // weight grad fused with the SGD step: a local expert's tile is applied straight to its bf16
@@ -230,6 +234,12 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
   }
   t.alloc = t.g >= p.split ? 1 : 0;
   t.g_local = t.alloc ? t.g - p.split : t.g;
+  if constexpr (WGRAD) {
+    if (p.wg_select != 0 && p.sgd_w != nullptr) {
+      const bool applied = t.alloc == 0 && (p.sgd_keep == nullptr || p.sgd_keep[t.g_local] == 0);
+      if ((p.wg_select == 2) != applied) t.valid = false;
+    }
+  }
   return t;
 }
 
@@ -700,7 +710,6 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
           }
           __syncwarp();
         }
-        __threadfence_system();   // pushed rows are ordered before this rank's next barrier arrival
       } else {
         bool row_ok;
         long long off_row;
@@ -931,6 +940,11 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
     while (globaltimer_ns() - t0 < 200000ull) { }
   }
   if (warp >= 2 && lane == 0) bulk_wait<0>();   // epilogue TMA stores have completed
+  // Pushed rows: the kernel that consumes them on the home rank runs behind a cross-rank barrier
+  // that this rank enters from a LATER launch of the same stream, so the end of this kernel
+  // already orders the stores; one fence here (instead of one per tile, which made every epilogue
+  // warp wait for an NVLink round trip per tile) keeps that independent of how the next launch arrives.
+  if constexpr (EPI == EPI_PUSH) { if (warp >= 2) __threadfence_system(); }
   if constexpr (TWO) cluster_sync_all();        // neither CTA leaves while its peer may still touch it
   if (warp == 1) {
     tc_fence_after();
@@ -960,7 +974,7 @@ struct GemmDesc {
   void* push_base;
   int64_t push_rank_stride;
   int32_t push_entries, push_ranks;
-  int32_t two_cta, pad2_;
+  int32_t two_cta, wg_select;
   void* sgd_w;
   const int32_t* sgd_keep;
   float sgd_lr;
@@ -1202,6 +1216,7 @@ int mep_gemm_launch(const GemmDesc* d, cudaStream_t stream) {
     }
     const bool pair = d->two_cta != 0 && grid >= 2 && d->Mw % (2 * BM) == 0;
     if (kp.sgd_w != nullptr) sgd_geometry(pair, &kp);
+    kp.wg_select = kp.sgd_w != nullptr ? d->wg_select : 0;
     if (kp.sgd_w != nullptr)
       return pair ? launch_gemm2<true, true, EPI_F32, true, true>(kp, grid, stream)
                   : launch_gemm<true, true, true, EPI_F32, true>(kp, grid, stream);

@@ -21,6 +21,7 @@ Weights are bf16, weight grads fp32 ("main grads"), written by the GEMM epilogue
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -247,26 +248,33 @@ class _MoEFn(torch.autograd.Function):
     @staticmethod
     def _late_wgrads(layer, plan, hidden, d_gate, d_up, cu, gslot, split, ev_r, do_reduce, sgd):
         """Fused-SGD order only: the gate / up weight grads (which update the weights in their
-        epilogues) run after dX; their replicas' grads then travel home under the combine and the
-        router backward.  Returns the event that covers every reduce launched so far."""
+        epilogues) run after dX.  Returns the event that covers every reduce launched so far."""
         if layer.fused_sgd_lr is None:
             return ev_r
         pools, zc = layer.pools, layer.accumulate_grads
+        wg = lambda a, g, w, **kw: gemm.wgrad(hidden, a, cu, g, grad_slot=gslot(w), split=split,
+                                              sgd=sgd(getattr(layer, "w_" + w)), **kw)
         with layer.tracer.span("b.wgrad_gateup"):
-            gemm.wgrad(hidden, d_gate, cu, layer.g_gate, grad_slot=gslot("gate"), split=split,
-                       sgd=sgd(layer.w_gate))
+            wg(d_gate, layer.g_gate, "gate")
             if do_reduce:     # the gate grads travel home under the up projection's weight grad
                 ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_gate], [pools.reduce["gate"]],
                                                      async_finish=True, zero_consumed=zc)
-            gemm.wgrad(hidden, d_up, cu, layer.g_up, grad_slot=gslot("up"), split=split, sgd=sgd(layer.w_up),
-                       grid=layer.overlap_grid() if do_reduce else 0)
+            if do_reduce and layer.split_last_wgrad:
+                # The up grads are the last to be computed, and only the combine and the router
+                # backward are left to cover their way home.  So the grads that have to travel
+                # (experts with replicas elsewhere, this rank's slot groups) are computed first, in
+                # a short launch of their own, and leave while the rest is computed and applied.
+                wg(d_up, layer.g_up, "up", select=1, grid=layer.overlap_grid())
+                ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
+                                                     async_finish=True, zero_consumed=zc)
+                wg(d_up, layer.g_up, "up", select=2, grid=layer.overlap_grid())
+            else:
+                wg(d_up, layer.g_up, "up", grid=layer.overlap_grid() if do_reduce else 0)
+                if do_reduce:
+                    ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
+                                                         async_finish=True, zero_consumed=zc)
         if layer.hidden_in_place:      # the forward rows have had their last reader
             layer.buf.release_second_shard(layer)
-        if do_reduce:         # and the up grads under the combine and the router backward, which
-            # leave most SMs idle: this last reduce is what the step waits for, give it more CTAs
-            ev_r = layer.buf.reduce_grad_tensors(plan, [layer.g_up], [pools.reduce["up"]],
-                                                 async_finish=True, zero_consumed=zc,
-                                                 num_sms=layer.last_reduce_sms)
         return ev_r
 
 
@@ -292,8 +300,12 @@ class MoELayer:
         # set to a learning rate to run the SGD step of the expert weights inside the weight-grad
         # epilogues of the next backward pass (see ``fuse_sgd``)
         self.fused_sgd_lr: Optional[float] = None
-        # CTAs of the step's last reduce_grad launch (0: the Buffer's num_sms_weights)
-        self.last_reduce_sms = max(buf.num_sms_weights, 48) // 2 * 2
+        # fused SGD: compute the up projection's travelling grads in a launch of their own, ahead
+        # of the rest (see ``_late_wgrads``).  Pays when the last reduce_grad of the step is long
+        # enough to stick out behind the combine and the router backward: measured exposed for
+        # 0.37 ms at 8 ranks, hidden at 2 and 4, where the extra launch would only cost.
+        _e = os.environ.get("MOONEP_B200_SPLIT_WGRAD", "").strip()
+        self.split_last_wgrad = (buf.R >= 8) if _e == "" else _e != "0"
         self._sgd_keep = None
         self.tracer = NULL_TRACER
         if fused_combine:

@@ -47,7 +47,7 @@ class _GemmDesc(ctypes.Structure):
         ("row_scale", ctypes.c_void_p), ("status", ctypes.c_void_p), ("timeout_ns", ctypes.c_int64),
         ("src_info", ctypes.c_void_p), ("push_base", ctypes.c_void_p),
         ("push_rank_stride", ctypes.c_int64), ("push_entries", ctypes.c_int32),
-        ("push_ranks", ctypes.c_int32), ("two_cta", ctypes.c_int32), ("pad2_", ctypes.c_int32),
+        ("push_ranks", ctypes.c_int32), ("two_cta", ctypes.c_int32), ("wg_select", ctypes.c_int32),
         ("sgd_w", ctypes.c_void_p), ("sgd_keep", ctypes.c_void_p), ("sgd_lr", ctypes.c_float),
         ("disp_mode", ctypes.c_int32), ("disp_ctx", ctypes.c_void_p), ("disp_x", ctypes.c_void_p),
         ("disp_w", ctypes.c_void_p), ("disp_dst", ctypes.c_void_p), ("disp_order", ctypes.c_void_p),
@@ -264,7 +264,7 @@ def gateup_dgrad(dg, du, wg, wu, cu_seqlens, *, wg_slot=None, wu_slot=None, spli
 
 
 def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulate=False, sgd=None,
-          grid=0):
+          grid=0, select=0):
     """``grad[g] (+)= a[rows of g]^T b[rows of g]``; ``a`` [rows, M], ``b`` [rows, N], fp32 grads
     ``[G0, M, N]`` (+ slot grads for groups >= split).  Group sizes must be multiples of 64
     (padding rows must be zero in ``a`` or ``b``).  Empty groups below ``split`` are zeroed
@@ -275,7 +275,12 @@ def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulat
     ``weights`` ``[G0, M, N]`` as ``w = bf16(w - lr * grad)``, bit-identical to ``sgd_update_`` on
     the stored grad, and ``grad_local`` is NOT written for that group.  Groups with a set flag and
     slot groups are stored as fp32 grads as usual.  This saves writing and re-reading the fp32
-    grad (8 of the 12 bytes per parameter that weight grad + SGD move)."""
+    grad (8 of the 12 bytes per parameter that weight grad + SGD move).
+
+    With ``sgd``, ``select=1`` computes only the groups whose grads are stored (set flags, slot
+    groups) and ``select=2`` only the ones that are applied; the two launches together equal one
+    with ``select=0``.  The stored grads are the ones that ``reduce_grad`` has to move, so computing
+    them first lets that transfer run beside the rest of the weight grad."""
     _bf16(a, "a"), _bf16(b, "b")
     rows, M = a.shape
     N = b.shape[1]
@@ -306,6 +311,7 @@ def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulat
         _bf16(w, "weights")
         assert not accumulate and w.is_contiguous() and w.shape == grad_local.shape and N % 8 == 0
         d.sgd_w, d.sgd_lr = w.data_ptr(), float(lr)
+        d.wg_select = int(select)
         if keep is not None:
             assert keep.dtype == torch.int32 and keep.is_cuda and keep.numel() >= min(d.split, ngroups)
             d.sgd_keep = keep.data_ptr()

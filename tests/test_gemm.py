@@ -209,3 +209,35 @@ def test_weight_grad_fused_sgd(two, monkeypatch):
     assert torch.equal(gs2[0], gs[0]) and bool((gs2[1] == 7.0).all())         # slots: stored / empty untouched
     ew.sgd_update_(w, gl2, lr, only=keep)
     assert torch.equal(w, want)
+
+
+@pytest.mark.parametrize("two", [0, 1])
+def test_weight_grad_fused_sgd_in_two_launches(two, monkeypatch):
+    """``select=1`` (stored grads only) followed by ``select=2`` (applied tiles only) leaves exactly
+    what one launch leaves; after the first launch no weight has changed yet."""
+    from moonep_b200.ops import gemm
+    monkeypatch.setattr(gemm, "TWO_CTA", two)
+    g = torch.Generator(device="cuda").manual_seed(14)
+    groups = [128, 256, 0, 64, 192, 64]
+    ends, rows = _mk(groups)
+    M, N, split, lr = 256, 264, 4, 0.21
+    a = torch.randn(rows, M, device="cuda", generator=g).bfloat16()
+    b = torch.randn(rows, N, device="cuda", generator=g).bfloat16()
+    w0 = torch.randn(split, M, N, device="cuda", generator=g).bfloat16()
+    keep = torch.tensor([1, 0, 0, 1], dtype=torch.int32, device="cuda")
+    outs = []
+    for selects in ((0,), (1, 2)):
+        w = w0.clone()
+        gl = torch.full((split, M, N), 5.0, device="cuda")
+        gs = torch.full((len(groups) - split, M, N), 5.0, device="cuda")
+        for i, sel in enumerate(selects):
+            gemm.wgrad(a, b, ends, gl, grad_slot=gs, split=split, sgd=(w, lr, keep), select=sel)
+            if sel == 1:
+                torch.cuda.synchronize()
+                assert torch.equal(w, w0)                       # nothing applied yet
+                assert not bool((gl[0] == 5.0).all()) and not bool((gs[0] == 5.0).all())
+        torch.cuda.synchronize()
+        outs.append((w, gl, gs))
+    for x, y in zip(*outs):
+        assert torch.equal(x, y)
+    gemm.check_status()
