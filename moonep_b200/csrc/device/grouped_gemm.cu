@@ -25,7 +25,9 @@
 //        D[g] (+)= A[rows of g]^T * B[rows of g]   both operands MN-major, fp32 output by TMA
 //        store / reduce-add; or (template SGD) the optimizer step fused in: the accumulator is
 //        applied straight to the bf16 weights, w = bf16(w - lr * acc), through a per-warp TMA
-//        ring of weight blocks, for every local expert that has no replica this step.
+//        ring of weight blocks, for every local expert that has no replica this step.  Those
+//        kernels run eight epilogue warps (two per quarter of the accumulator's lanes, one half
+//        of the columns each) and take their split of the shared memory at launch.
 // Group g < split reads/writes allocation 0 (local experts), g >= split allocation 1 (this
 // rank's prefetch / reduce slots): the [2*epn] compute view never has to be contiguous.
 // CTA pairs (template TWO, clusters of two CTAs, tcgen05 cta_group::2): the leader issues
@@ -243,21 +245,21 @@ __device__ __forceinline__ Tile get_tile(const GemmKParams& p, int id, const int
   return t;
 }
 
-// SGD (weight grad only): the optimizer step is fused into the epilogue.  That variant gives up
-// one stage of the operand ring for a ring of weight blocks per epilogue warp (see the epilogue).
-template <bool TWO, bool SGD, bool DISP = false> __host__ __device__ constexpr int gemm_stages() {
-  return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (SGD ? 1 : 0) - (DISP ? 1 : 0);
+// Operand stages of the kernels whose geometry is fixed at compile time; the fused dispatch gives
+// one up for its copy ring.
+template <bool TWO, bool DISP = false> __host__ __device__ constexpr int gemm_stages() {
+  return (TWO ? GEMM_STAGES2 : GEMM_STAGES) - (DISP ? 1 : 0);
 }
-// The SGD kernels take their ring geometry at launch (GemmKParams::stages / wb): how the shared
-// memory is best split between operand stages and weight blocks depends on the group length.
+// The SGD kernels (weight grad with the optimizer step in the epilogue) take their geometry at
+// launch instead (GemmKParams::stages / wb, sgd_geometry() below): how the shared memory is best
+// split between operand stages and weight blocks depends on the group length.
 constexpr int SGD_RING_MAX = 8;      // 4 KB weight blocks per epilogue warp, at most
-template <bool TWO> __host__ __device__ constexpr int sgd_ring() { return TWO ? 2 : 3; }   // geometry of gemm_smem<.., SGD>()
 // Fused dispatch: stages of the copy ring (the pair kernel with the staged bf16 epilogue has less
 // shared memory to spare).
 template <bool TWO, int EPI> __host__ __device__ constexpr int fd_stages() { return (TWO && EPI == EPI_BF16) ? 5 : 8; }
-template <bool TWO, bool SGD, bool DISP = false, int EPI = EPI_BF16> __host__ __device__ constexpr int gemm_smem() {   // dynamic shared memory
-  return gemm_stages<TWO, SGD, DISP>() * (TWO ? STAGE_BYTES2 : STAGE_BYTES) + 1024 +
-         (SGD ? 4 * sgd_ring<TWO>() * 4096 : 0) + (DISP ? fd_stages<TWO, EPI>() * FD_PART_CAP : 0);
+template <bool TWO, bool DISP = false, int EPI = EPI_BF16> __host__ __device__ constexpr int gemm_smem() {   // dynamic shared memory
+  return gemm_stages<TWO, DISP>() * (TWO ? STAGE_BYTES2 : STAGE_BYTES) + 1024 +
+         (DISP ? fd_stages<TWO, EPI>() * FD_PART_CAP : 0);
 }
 
 template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool TWO = false, bool SGD = false, bool DISP = false>
@@ -266,7 +268,7 @@ ep_grouped_gemm_kernel(const __grid_constant__ GemmKParams p) {
   static_assert(!SGD || (WGRAD && EPI == EPI_F32), "the fused SGD step belongs to the weight grad");
   static_assert(!DISP || (!WGRAD && !SGD), "the fused dispatch feeds a token-major GEMM");
   // operand stages: a constant, except in the SGD kernels (upper bound; p.stages are used)
-  constexpr int GEMM_STAGES = SGD ? (TWO ? GEMM_STAGES2 : mep::GEMM_STAGES) : gemm_stages<TWO, false, DISP>();
+  constexpr int GEMM_STAGES = SGD ? (TWO ? GEMM_STAGES2 : mep::GEMM_STAGES) : gemm_stages<TWO, DISP>();
   const int nst = SGD ? p.stages : GEMM_STAGES;
   constexpr int FD_NST = fd_stages<TWO, EPI>();
   constexpr int STAGE_BYTES = TWO ? STAGE_BYTES2 : mep::STAGE_BYTES;
@@ -1079,7 +1081,7 @@ static int sgd_smem_limit(const void* kern) {
 template <bool A_MN, bool B_MN, int EPI, bool WGRAD = false, bool SGD = false, bool DISP = false>
 static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
   auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, true, SGD, DISP>;
-  const int GEMM_SMEM2 = SGD ? sgd_smem(kp, true) : gemm_smem<true, SGD, DISP, EPI>();
+  const int GEMM_SMEM2 = SGD ? sgd_smem(kp, true) : gemm_smem<true, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
     const int most = SGD ? sgd_smem_limit((const void*)kern) : GEMM_SMEM2;
@@ -1133,7 +1135,7 @@ static int launch_gemm2(const GemmKParams& kp, int grid, cudaStream_t stream) {
 template <bool WGRAD, bool A_MN, bool B_MN, int EPI, bool SGD = false, bool DISP = false>
 static int launch_gemm(const GemmKParams& kp, int grid, cudaStream_t stream) {
   auto kern = ep_grouped_gemm_kernel<WGRAD, A_MN, B_MN, EPI, false, SGD, DISP>;
-  const int GEMM_SMEM = SGD ? sgd_smem(kp, false) : gemm_smem<false, SGD, DISP, EPI>();
+  const int GEMM_SMEM = SGD ? sgd_smem(kp, false) : gemm_smem<false, DISP, EPI>();
   static bool configured = false;
   if (!configured) {
     const int most = SGD ? sgd_smem_limit((const void*)kern) : GEMM_SMEM;
