@@ -344,6 +344,7 @@ def run_ours(args):
                    "dispatch": "inside the gate/up and down-dgrad GEMM launches (rows consumed as they arrive)"
                    if layer.fused_dispatch else "stand-alone kernel + barrier before the GEMM",
                    "combine": "pull" if args.no_fused_combine else "pushed by the GEMM epilogue",
+                   "last_weight_grad": "two launches, travelling grads first" if layer.split_last_wgrad else "one launch",
                    "cuda_graph": graphed,
                    "l2": "working set per step (>= 8 GB of weights, grads and activations) exceeds the 126 MB L2; no explicit flush"},
         "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
