@@ -306,6 +306,7 @@ def wgrad(a, b, cu_seqlens, grad_local, *, grad_slot=None, split=None, accumulat
         assert d.split >= ngroups
     d.ldc = N
     d.grid = grid
+    assert select in (0, 1, 2) and (select == 0 or sgd is not None), "select splits a fused-SGD weight grad"
     if sgd is not None:
         w, lr, keep = sgd
         _bf16(w, "weights")
